@@ -28,6 +28,8 @@ extern "C" {
 #define KLLM_SEQ_MIXER_ATTENTION 1 /* softmax attention over the sequence's cached keys */
 #define KLLM_SEQ_MIXER_LATENT 2    /* softmax attention through a low-rank latent: only the latent and one rotated key part are cached */
 #define KLLM_SEQ_MIXER_LINEAR 3    /* linear attention with a decayed matrix state per head (no cache, a recurrent state) */
+#define KLLM_SEQ_MIXER_SSM 4       /* selective scan: short convolution, input-dependent step sizes, a diagonal state per channel */
+#define KLLM_SEQ_MIXER_DELTA 5     /* gated delta rule: a matrix state per head, decayed per key channel and corrected towards each value */
 #define KLLM_SEQ_FF_NONE 0
 #define KLLM_SEQ_FF_MOE 1   /* routed experts (softmax or sigmoid router), optional gated shared expert */
 #define KLLM_SEQ_FF_DENSE 2 /* down(act(up h)) */
@@ -39,9 +41,15 @@ extern "C" {
 #define KLLM_SEQ_ACT_SWIGLU 0 /* silu(gate h) * (up h): the weights hold gate rows, then up rows */
 #define KLLM_SEQ_ACT_RELU2 1  /* max(up h, 0)^2 */
 #define KLLM_SEQ_ACT_XIELU 2  /* z > 0: a z^2 + z / 2;  z <= 0: b (exp(z) - 1 - z) + z / 2 */
+#define KLLM_SEQ_ACT_RELU_GATE 3    /* max(gate h, 0) * (up h): gate rows, then up rows */
+#define KLLM_SEQ_ACT_CLAMP_SWIGLU 4 /* g = min(gate h, limit), u = clamp(up h, -limit, limit): g * sigmoid(alpha g) * (u + 1) */
 
 #define KLLM_SEQ_ROUTER_SOFTMAX 0 /* scores = softmax(z); weights = chosen scores / their sum * scale */
 #define KLLM_SEQ_ROUTER_SIGMOID 1 /* scores = sigmoid(z); chosen by score + correction, inside the best groups; weights = score * scale */
+#define KLLM_SEQ_ROUTER_TOP_SOFTMAX 2 /* the largest logits are chosen; weights = softmax over the chosen logits only, * scale */
+
+#define KLLM_SEQ_ROPE_HALVES 0 /* coordinate i is rotated with coordinate i + dims / 2 */
+#define KLLM_SEQ_ROPE_PAIRS 1  /* coordinate 2i is rotated with coordinate 2i + 1 */
 
 typedef struct kllm_seq_norm {
   const float* w; /* [width] */
@@ -60,6 +68,18 @@ typedef struct kllm_seq_attention {
   const float* q_norm_w; /* [dim] */
   const float* k_norm_w; /* [dim] */
   const void* w_out;     /* [width, heads*vdim], compute type */
+  int32_t window;        /* position i sees j <= i with i - j < window or j < keep_first; 0: every earlier position */
+  int32_t keep_first;    /* the first keep_first positions stay visible behind the window (at their true positions) */
+  float softcap;         /* score <- softcap * tanh(score / softcap) after the scale; 0: none */
+  const float* sink;     /* [heads]: exp(sink) joins the softmax denominator (no key, no value), or NULL */
+  const float* in_bias;  /* [rows of w_in] fp32 added to the projection, or NULL */
+  int32_t conv_taps;     /* > 1: a causal convolution over time on every query and key channel, right after the projection
+                            (zeros before the sequence's start; the last conv_taps - 1 projected rows are state of the sequence) */
+  const float* conv_w;   /* [heads*dim + kv_heads*dim][conv_taps] fp32, the last column weighs the current token */
+  int32_t rope_dims;     /* rotary positions on the first rope_dims coordinates of every query and key head; 0: none */
+  float rope_base;       /* angle of pair i = position * rope_base^(-2 i / rope_dims) */
+  int32_t rope_pairing;  /* KLLM_SEQ_ROPE_* */
+  int32_t values_are_keys; /* the values are the keys as they are before the rotation: w_in has no value rows, vdim == dim */
 } kllm_seq_attention;
 
 /* Attention through a latent.  Queries: cq = RMSnorm(W_dq h), q = W_uq cq, per head [dim plain | rot_dim rotated].
@@ -92,8 +112,41 @@ typedef struct kllm_seq_linear {
   const void* w_out;       /* [width, heads * vdim] */
 } kllm_seq_linear;
 
+/* Selective scan.  W_in h = [u | z] (inner each); u <- silu(conv(u) + conv_b); W_x u = [low: dt_rank | B: state | C: state];
+ * step d = softplus(W_dt low + dt_b) per channel; per channel c and state n: S <- exp(d_c a[c, n]) S + d_c u_c B_n;
+ * y_c = sum_n S[c, n] C_n + D_c u_c; out = W_out (y * silu(z)).  S and the last conv_taps - 1 rows of u are fp32 state. */
+typedef struct kllm_seq_ssm {
+  int32_t inner, state, dt_rank, conv_taps;
+  const void* w_in;     /* [2 * inner, width]: u rows, then z rows */
+  const float* conv_w;  /* [inner][conv_taps] fp32, the last column weighs the current token */
+  const float* conv_b;  /* [inner] or NULL */
+  const void* w_x;      /* [dt_rank + 2 * state, inner] */
+  const float* w_dt;    /* [inner, dt_rank] fp32 */
+  const float* dt_b;    /* [inner] */
+  const float* a;       /* [inner, state] fp32: the rates, already negative (-exp(A_log)) */
+  const float* d;       /* [inner] */
+  const void* w_out;    /* [width, inner] */
+} kllm_seq_ssm;
+
+/* Gated delta rule.  q, k (kv_heads x dim) and v (heads x vdim) = silu(conv(W h)); q, k <- unit vectors per head
+ * (x / sqrt(sum x^2 + 1e-6)), q *= dim^-1/2; beta = sigmoid(W_b h) per head; decay g = exp(-rate_h * softplus(W_a2 (W_a1 h) +
+ * dt_bias)) per head and key channel.  Per head: S <- g * S (rows); u = beta (v - S^T k); S <- S + k u^T; o = S^T q.
+ * o / rms(o) * out_norm_w * sigmoid(W_g2 (W_g1 h)), then W_out.  S [dim, vdim] per head and the last conv_taps - 1
+ * projected rows are fp32 state.  Head h reads q / k head h / (heads / kv_heads). */
+typedef struct kllm_seq_delta {
+  int32_t heads, kv_heads, dim, vdim, conv_taps, decay_rank, gate_rank;
+  const void* w_in;        /* [2 * kv_heads*dim + heads*vdim + heads + decay_rank + gate_rank, width]: q | k | v | beta | a1 | g1 rows */
+  const float* conv_w;     /* [2 * kv_heads*dim + heads*vdim][conv_taps] fp32 */
+  const float* w_a2;       /* [heads*dim, decay_rank] fp32 */
+  const float* dt_bias;    /* [heads*dim] */
+  const float* rate;       /* [heads] fp32: exp(A_log) */
+  const float* w_g2;       /* [heads*vdim, gate_rank] fp32 */
+  const float* out_norm_w; /* [vdim] */
+  const void* w_out;       /* [width, heads*vdim] */
+} kllm_seq_delta;
+
 typedef struct kllm_seq_dense {
-  int32_t ff, act;    /* inner size; KLLM_SEQ_ACT_* (XIELU or RELU2) */
+  int32_t ff, act;    /* inner size; KLLM_SEQ_ACT_* (XIELU, RELU2, or RELU_GATE: then `up` holds ff gate rows followed by ff up rows) */
   float act_a, act_b; /* the two coefficients of KLLM_SEQ_ACT_XIELU */
   const void* up;     /* [ff, width] */
   const void* down;   /* [width, ff] */
@@ -113,7 +166,10 @@ typedef struct kllm_seq_moe {
   const float* correction;    /* [experts] added to the scores for the choice only (sigmoid router), or NULL */
   int32_t groups, groups_keep; /* sigmoid router: experts form `groups` equal groups of neighbours, a group scores the sum
                                   of its two largest choice scores, and only the best groups_keep groups can be chosen; 0: no groups */
-  int32_t act;                /* KLLM_SEQ_ACT_SWIGLU, or KLLM_SEQ_ACT_RELU2 (then gate_up holds [experts][ff][width]) */
+  int32_t act;                /* KLLM_SEQ_ACT_SWIGLU / CLAMP_SWIGLU, or KLLM_SEQ_ACT_RELU2 (then gate_up holds [experts][ff][width]) */
+  const float* router_bias;   /* [experts] fp32 added to the router's logits, or NULL */
+  float act_limit, act_alpha; /* KLLM_SEQ_ACT_CLAMP_SWIGLU: the routed experts' clamp and the sigmoid's slope */
+  float shared_act_limit;     /* the shared expert's clamp (same activation and slope) */
 } kllm_seq_moe;
 
 typedef struct kllm_seq_layer {
@@ -130,6 +186,15 @@ typedef struct kllm_seq_layer {
   kllm_seq_latent latent;
   kllm_seq_linear linear;
   kllm_seq_dense dense;
+  kllm_seq_ssm ssm;
+  kllm_seq_delta delta;
+  /* A second mixer of another kind beside the first (0: none): both read the same input and the mixer's output is
+   * mixer_scale * first + mixer2_scale * second. */
+  int32_t mixer2_kind;
+  float mixer_scale, mixer2_scale;
+  /* != 0: the feed-forward reads the mixer's input too (pre_mixer's output; pre_ff is not used) and
+   * x += mixer(...) + ff(...) in one step */
+  int32_t parallel_ff;
 } kllm_seq_layer;
 
 typedef struct kllm_seq_desc {
@@ -155,6 +220,8 @@ typedef struct kllm_seq_desc {
   const int32_t* run_embed;  /* [n_runs] or NULL: != 0 adds the embedding output (after embed_norm) to the residual stream
                                 before the run, ahead of run_add's vector */
   float logit_scale;         /* logits = head(...) * logit_scale; 0 means 1 */
+  float embed_scale;         /* the embedding rows are multiplied by it (before embed_norm); 0 means 1 */
+  float logit_softcap;       /* logits <- cap * tanh(logits / cap), after logit_scale; 0: none */
 } kllm_seq_desc;
 
 typedef struct kllm_seq_engine kllm_seq_engine;

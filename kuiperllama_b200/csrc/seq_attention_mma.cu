@@ -110,8 +110,15 @@ attention_mma_kernel(AttnShape a, const __nv_bfloat16* __restrict__ q, PagedKV k
   // with a window the first row of the tile sees nothing before its position - window + 1
   const int window = a.window;
   const int tile_first = window > 0 ? max(0, pos0 + r0 / rep - window + 1) / kKeys : 0;
-  const int per = (n_tiles - tile_first + splits - 1) / splits;
-  const int tile_lo = tile_first + split * per, tile_hi = min(n_tiles, tile_lo + per);
+  // tiles before the window that hold kept first positions come ahead of the window's tiles: this CTA's list of tiles
+  // is [0, keep_tiles) then [tile_first, n_tiles), cut into `splits` parts
+  const int keep_first = window > 0 ? a.keep_first : 0;
+  const int keep_tiles = min(tile_first, (keep_first + kKeys - 1) / kKeys);
+  const int list_n = keep_tiles + n_tiles - tile_first;
+  const int per = (list_n + splits - 1) / splits;
+  const int tile_lo = split * per, tile_hi = min(list_n, tile_lo + per);
+  auto tile_of = [&](int li) { return li < keep_tiles ? li : tile_first + (li - keep_tiles); };
+  const float softcap = a.softcap;
 
   extern __shared__ __align__(16) unsigned char sm_raw[];
   __nv_bfloat16* Ks = reinterpret_cast<__nv_bfloat16*>(sm_raw);  // [2][keys][LDK]
@@ -128,7 +135,7 @@ attention_mma_kernel(AttnShape a, const __nv_bfloat16* __restrict__ q, PagedKV k
   const int warp_last = __reduce_max_sync(0xffffffffu, max(posA, posB));  // last position any row of the warp sees
   // first position of the warp's rows (rows that do not exist count as -1: their tiles are always masked)
   const int warp_first = __reduce_min_sync(0xffffffffu, min(posA, posB));
-  const float scale2 = a.scale * 1.4426950408889634f;  // scores are kept in units of log2: exp(x) = 2^(x log2 e)
+  const float scale2_plain = a.scale * 1.4426950408889634f;  // scores are kept in units of log2: exp(x) = 2^(x log2 e)
 
   uint32_t qf[KS][4];
   {
@@ -177,11 +184,12 @@ attention_mma_kernel(AttnShape a, const __nv_bfloat16* __restrict__ q, PagedKV k
     cp_async_commit();
   };
 
-  if (tile_lo < tile_hi) load_tile(tile_lo, 0);
-  for (int tile = tile_lo; tile < tile_hi; ++tile) {
-    const int stage = (tile - tile_lo) & 1;
-    if (tile + 1 < tile_hi) {
-      load_tile(tile + 1, stage ^ 1);
+  if (tile_lo < tile_hi) load_tile(tile_of(tile_lo), 0);
+  for (int li = tile_lo; li < tile_hi; ++li) {
+    const int tile = tile_of(li);
+    const int stage = (li - tile_lo) & 1;
+    if (li + 1 < tile_hi) {
+      load_tile(tile_of(li + 1), stage ^ 1);
       cp_async_wait<1>();
     } else {
       cp_async_wait<0>();
@@ -189,7 +197,7 @@ attention_mma_kernel(AttnShape a, const __nv_bfloat16* __restrict__ q, PagedKV k
     __syncthreads();
     const int k0 = tile * kKeys;
     // otherwise no row of this warp sees a key of the tile (all later, or all before every row's window)
-    if (k0 <= warp_last && (window == 0 || k0 + kKeys - 1 > warp_first - window)) {
+    if (k0 <= warp_last && (window == 0 || k0 + kKeys - 1 > warp_first - window || k0 < keep_first)) {
       float s[kKeys / 8][4];
 #pragma unroll
       for (int j = 0; j < kKeys / 8; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
@@ -207,6 +215,14 @@ attention_mma_kernel(AttnShape a, const __nv_bfloat16* __restrict__ q, PagedKV k
             mma_bf16(s[j], qf[ks + 1], b2, b3);
           }
       }
+      if (softcap > 0.f) {  // capped scores, then into units of log2 (the scale2 below is replaced by log2 e)
+        const float inv = a.scale / softcap;
+#pragma unroll
+        for (int j = 0; j < kKeys / 8; ++j)
+#pragma unroll
+          for (int c = 0; c < 4; ++c) s[j][c] = softcap * tanhf(s[j][c] * inv);
+      }
+      const float scale2 = softcap > 0.f ? 1.4426950408889634f : scale2_plain;
       float mxA = -INFINITY, mxB = -INFINITY;
       if (k0 + kKeys - 1 <= warp_first && (window == 0 || warp_last - k0 < window)) {  // every row of the warp sees the whole tile
 #pragma unroll
@@ -220,10 +236,10 @@ attention_mma_kernel(AttnShape a, const __nv_bfloat16* __restrict__ q, PagedKV k
         for (int j = 0; j < kKeys / 8; ++j) {
           const int kj = k0 + j * 8 + t4 * 2;
           const int loA = window > 0 ? posA - window : -1, loB = window > 0 ? posB - window : -1;  // the last key not seen
-          s[j][0] = kj <= posA && kj > loA ? s[j][0] * scale2 : -INFINITY;
-          s[j][1] = kj + 1 <= posA && kj + 1 > loA ? s[j][1] * scale2 : -INFINITY;
-          s[j][2] = kj <= posB && kj > loB ? s[j][2] * scale2 : -INFINITY;
-          s[j][3] = kj + 1 <= posB && kj + 1 > loB ? s[j][3] * scale2 : -INFINITY;
+          s[j][0] = kj <= posA && (kj > loA || kj < keep_first) ? s[j][0] * scale2 : -INFINITY;
+          s[j][1] = kj + 1 <= posA && (kj + 1 > loA || kj + 1 < keep_first) ? s[j][1] * scale2 : -INFINITY;
+          s[j][2] = kj <= posB && (kj > loB || kj < keep_first) ? s[j][2] * scale2 : -INFINITY;
+          s[j][3] = kj + 1 <= posB && (kj + 1 > loB || kj + 1 < keep_first) ? s[j][3] * scale2 : -INFINITY;
           mxA = fmaxf(mxA, fmaxf(s[j][0], s[j][1]));
           mxB = fmaxf(mxB, fmaxf(s[j][2], s[j][3]));
         }

@@ -101,6 +101,9 @@ struct kllm_seq_engine {
   // matrix state of linear attention [max_seqs][heads][dim][vdim]; fp32.  A sequence's state is taken as zero while its
   // length is 0, so a slot that is used again needs no clearing.
   std::vector<float*> shift_state, linear_state;
+  // more state per run and slot (fp32): the last taps - 1 inputs of the short convolutions of an attention, a selective
+  // scan and a delta rule; the diagonal state of the scan [max_seqs][inner][state]; the delta rule's [max_seqs][heads][dim][vdim]
+  std::vector<float*> attn_conv, ssm_conv, ssm_state, delta_conv, delta_state;
   int32_t* table_dev = nullptr;       // [max_seqs][table_stride]
   std::vector<int32_t> table_host;
   std::vector<int32_t> free_pages;    // kept sorted descending: back() is the lowest number
@@ -116,6 +119,8 @@ struct kllm_seq_engine {
   DevBuf idx, x, h, proj, q, gates, att, y, y2, ws, top_idx, top_w, sgate, inter, pairs_out, sort, sorted_a, sorted_inter, hw, logits, amax;
   DevBuf lat_c, lat_kr, lat_kp, lat_vp, lat_q, lat_k, lat_v;  // a prompt step's latents expanded into per-head keys / values
   DevBuf x0, hn, qf, qa, ol;  // embedding output; fp32 normed rows ahead of a token shift; latent / linear attention scratch
+  DevBuf y3, y4;              // outputs of a second mixer and of a feed-forward that runs beside the mixer
+  DevBuf rec_a, rec_b;        // fp32 scratch of the selective scan (filtered rows, low-rank rows) and the delta rule (prepared rows)
   float* logits_pinned = nullptr;
   size_t logits_pinned_cap = 0;
   float* trace_host = nullptr;
@@ -147,7 +152,8 @@ struct kllm_seq_engine {
   }
   // limits over the layers
   int max_proj = 0, max_q = 0, max_att = 0, max_heads = 0, max_top = 0, max_ff = 0, max_sff = 0;
-  int max_qf = 0, max_qa = 0, max_ol = 0;
+  int max_qf = 0, max_qa = 0, max_ol = 0, max_rec_a = 0, max_rec_b = 0;
+  bool any_mixer2 = false, any_parallel_ff = false;
   bool any_shift = false, any_run_embed = false;
   std::vector<int32_t> run_embed;
 
@@ -156,6 +162,8 @@ struct kllm_seq_engine {
     for (void* p : v_pool) if (p) cudaFree(p);
     for (float* p : shift_state) if (p) cudaFree(p);
     for (float* p : linear_state) if (p) cudaFree(p);
+    for (auto* v : {&attn_conv, &ssm_conv, &ssm_state, &delta_conv, &delta_state})
+      for (float* p : *v) if (p) cudaFree(p);
     if (table_dev) cudaFree(table_dev);
     if (pinned) cudaFreeHost(pinned);
     if (logits_pinned) cudaFreeHost(logits_pinned);
@@ -164,6 +172,53 @@ struct kllm_seq_engine {
     if (own_stream && stream) cudaStreamDestroy(stream);
   }
 };
+
+static bool has_cache(int kind) { return kind == KLLM_SEQ_MIXER_ATTENTION || kind == KLLM_SEQ_MIXER_LATENT; }
+
+static int validate_mixer(const kllm_seq_layer& L, int kind) {
+  if (kind == KLLM_SEQ_MIXER_ATTENTION) {
+    const kllm_seq_attention& a = L.attn;
+    if (a.heads <= 0 || a.kv_heads <= 0 || a.heads % a.kv_heads || a.dim <= 0 || a.vdim <= 0 || !a.w_in || !a.w_out)
+      return KLLM_E_INVALID;
+    if (a.qk_norm && (!a.q_norm_w || !a.k_norm_w)) return KLLM_E_INVALID;
+    if (a.vdim > 256 || a.dim > 512) return KLLM_E_UNSUPPORTED;
+    if (a.window < 0 || a.keep_first < 0 || a.softcap < 0.f || a.conv_taps < 0 || a.rope_dims < 0 || a.rope_dims > a.dim ||
+        (a.rope_dims & 1) || (a.rope_dims > 0 && a.rope_base <= 0.f) || (a.conv_taps > 1 && !a.conv_w))
+      return KLLM_E_INVALID;
+    if (a.values_are_keys && a.vdim != a.dim) return KLLM_E_INVALID;
+    // the filtered, rotated form has its own preparation kernel: no head norms, temperature or gate there
+    const bool prep2 = a.values_are_keys || a.conv_taps > 1 || a.rope_dims > 0 || a.in_bias;
+    if (prep2 && (!a.values_are_keys || a.qk_norm || a.gate || a.temp_every)) return KLLM_E_UNSUPPORTED;
+  } else if (kind == KLLM_SEQ_MIXER_LATENT) {
+    const kllm_seq_latent& a = L.latent;
+    if (a.heads <= 0 || a.dim <= 0 || a.rot_dim < 0 || a.vdim <= 0 || a.q_rank <= 0 || a.kv_rank <= 0 || a.window < 0 ||
+        a.rope_dims < 0 || a.rope_dims > a.rot_dim || (a.rope_dims & 1) || (a.rope_dims > 0 && a.rope_base <= 0.f) ||
+        !a.w_in || !a.q_norm_w || !a.kv_norm_w || !a.w_uq || !a.w_uk || !a.w_uv || !a.w_out)
+      return KLLM_E_INVALID;
+    // the latent is the value of the paged attention kernel, latent + rotated part its key
+    if (a.kv_rank > 256 || a.kv_rank + a.rot_dim > 512) return KLLM_E_UNSUPPORTED;
+  } else if (kind == KLLM_SEQ_MIXER_LINEAR) {
+    const kllm_seq_linear& a = L.linear;
+    if (a.heads <= 0 || a.dim <= 0 || a.vdim <= 0 || !a.decay || !a.w_in || !a.out_norm_w || !a.w_out) return KLLM_E_INVALID;
+    if (a.dim > 256) return KLLM_E_UNSUPPORTED;
+  } else if (kind == KLLM_SEQ_MIXER_SSM) {
+    const kllm_seq_ssm& a = L.ssm;
+    if (a.inner <= 0 || a.state <= 0 || a.dt_rank <= 0 || a.conv_taps < 1 || !a.w_in || (a.conv_taps > 1 && !a.conv_w) ||
+        !a.w_x || !a.w_dt || !a.dt_b || !a.a || !a.d || !a.w_out)
+      return KLLM_E_INVALID;
+    if (a.state > 128) return KLLM_E_UNSUPPORTED;
+  } else if (kind == KLLM_SEQ_MIXER_DELTA) {
+    const kllm_seq_delta& a = L.delta;
+    if (a.heads <= 0 || a.kv_heads <= 0 || a.heads % a.kv_heads || a.dim <= 0 || a.vdim <= 0 || a.conv_taps < 1 ||
+        a.decay_rank <= 0 || a.gate_rank <= 0 || !a.w_in || (a.conv_taps > 1 && !a.conv_w) || !a.w_a2 || !a.dt_bias ||
+        !a.rate || !a.w_g2 || !a.out_norm_w || !a.w_out)
+      return KLLM_E_INVALID;
+    if (a.dim > 1024) return KLLM_E_UNSUPPORTED;
+  } else {
+    return KLLM_E_UNSUPPORTED;
+  }
+  return 0;
+}
 
 static int validate(const kllm_seq_desc* d) {
   if (!d || d->width <= 0 || d->vocab <= 0 || d->n_layers <= 0 || !d->layers || d->n_runs <= 0 || !d->run_layer ||
@@ -177,41 +232,30 @@ static int validate(const kllm_seq_desc* d) {
   for (int i = 0; i < d->n_layers; ++i) {
     const kllm_seq_layer& L = d->layers[i];
     if (!L.pre_mixer.w) return KLLM_E_INVALID;
-    if (L.mixer_kind == KLLM_SEQ_MIXER_ATTENTION) {
-      const kllm_seq_attention& a = L.attn;
-      if (a.heads <= 0 || a.kv_heads <= 0 || a.heads % a.kv_heads || a.dim <= 0 || a.vdim <= 0 || !a.w_in || !a.w_out)
-        return KLLM_E_INVALID;
-      if (a.qk_norm && (!a.q_norm_w || !a.k_norm_w)) return KLLM_E_INVALID;
-      if (a.vdim > 256 || a.dim > 512) return KLLM_E_UNSUPPORTED;
-    } else if (L.mixer_kind == KLLM_SEQ_MIXER_LATENT) {
-      const kllm_seq_latent& a = L.latent;
-      if (a.heads <= 0 || a.dim <= 0 || a.rot_dim < 0 || a.vdim <= 0 || a.q_rank <= 0 || a.kv_rank <= 0 || a.window < 0 ||
-          a.rope_dims < 0 || a.rope_dims > a.rot_dim || (a.rope_dims & 1) || (a.rope_dims > 0 && a.rope_base <= 0.f) ||
-          !a.w_in || !a.q_norm_w || !a.kv_norm_w || !a.w_uq || !a.w_uk || !a.w_uv || !a.w_out)
-        return KLLM_E_INVALID;
-      // the latent is the value of the paged attention kernel, latent + rotated part its key
-      if (a.kv_rank > 256 || a.kv_rank + a.rot_dim > 512) return KLLM_E_UNSUPPORTED;
-    } else if (L.mixer_kind == KLLM_SEQ_MIXER_LINEAR) {
-      const kllm_seq_linear& a = L.linear;
-      if (a.heads <= 0 || a.dim <= 0 || a.vdim <= 0 || !a.decay || !a.w_in || !a.out_norm_w || !a.w_out) return KLLM_E_INVALID;
-      if (a.dim > 256) return KLLM_E_UNSUPPORTED;
-    } else {
-      return KLLM_E_UNSUPPORTED;
+    if (int rc = validate_mixer(L, L.mixer_kind)) return rc;
+    if (L.mixer2_kind != 0) {
+      // the two mixers of a layer are of different kinds (a layer describes one mixer of each), and only one keeps pages
+      if (L.mixer2_kind == L.mixer_kind || (has_cache(L.mixer_kind) && has_cache(L.mixer2_kind))) return KLLM_E_UNSUPPORTED;
+      if (int rc = validate_mixer(L, L.mixer2_kind)) return rc;
     }
+    if (L.parallel_ff && (L.shift || L.ff_kind == KLLM_SEQ_FF_NONE)) return KLLM_E_UNSUPPORTED;
     if (L.ff_kind == KLLM_SEQ_FF_MOE) {
       const kllm_seq_moe& m = L.moe;
       if (m.experts <= 0 || m.top <= 0 || m.top > m.experts || m.ff <= 0 || !m.w_router || !m.gate_up || !m.down ||
-          !L.pre_ff.w)
+          (!L.pre_ff.w && !L.parallel_ff))
         return KLLM_E_INVALID;
       if (m.shared_ff > 0 && (!m.shared_gate_up || !m.shared_down)) return KLLM_E_INVALID;
-      if (m.act != KLLM_SEQ_ACT_SWIGLU && (m.act != KLLM_SEQ_ACT_RELU2 || m.shared_ff > 0)) return KLLM_E_UNSUPPORTED;
-      if (m.router_kind != KLLM_SEQ_ROUTER_SOFTMAX && m.router_kind != KLLM_SEQ_ROUTER_SIGMOID) return KLLM_E_UNSUPPORTED;
+      if (m.act != KLLM_SEQ_ACT_SWIGLU && m.act != KLLM_SEQ_ACT_CLAMP_SWIGLU && (m.act != KLLM_SEQ_ACT_RELU2 || m.shared_ff > 0))
+        return KLLM_E_UNSUPPORTED;
+      if (m.router_kind != KLLM_SEQ_ROUTER_SOFTMAX && m.router_kind != KLLM_SEQ_ROUTER_SIGMOID &&
+          m.router_kind != KLLM_SEQ_ROUTER_TOP_SOFTMAX)
+        return KLLM_E_UNSUPPORTED;
       if (m.groups < 0 || (m.groups > 0 && (m.experts % m.groups != 0 || m.groups_keep <= 0 || m.groups_keep > m.groups)))
         return KLLM_E_INVALID;
     } else if (L.ff_kind == KLLM_SEQ_FF_DENSE) {
       const kllm_seq_dense& f = L.dense;
-      if (f.ff <= 0 || !f.up || !f.down || !L.pre_ff.w) return KLLM_E_INVALID;
-      if (f.act != KLLM_SEQ_ACT_XIELU && f.act != KLLM_SEQ_ACT_RELU2) return KLLM_E_UNSUPPORTED;
+      if (f.ff <= 0 || !f.up || !f.down || (!L.pre_ff.w && !L.parallel_ff)) return KLLM_E_INVALID;
+      if (f.act != KLLM_SEQ_ACT_XIELU && f.act != KLLM_SEQ_ACT_RELU2 && f.act != KLLM_SEQ_ACT_RELU_GATE) return KLLM_E_UNSUPPORTED;
     } else if (L.ff_kind != KLLM_SEQ_FF_NONE) {
       return KLLM_E_UNSUPPORTED;
     }
@@ -259,24 +303,37 @@ extern "C" int kllm_seq_create(const kllm_seq_desc* desc, void* stream, kllm_seq
   for (int r = 0; r < desc->n_runs; ++r) {
     const kllm_seq_layer& L = e->layers[e->run_layer[r]];
     void *k = nullptr, *v = nullptr;
-    float *sh = nullptr, *ls = nullptr;
+    float *sh = nullptr, *ls = nullptr, *ac = nullptr, *sc = nullptr, *ss = nullptr, *dc = nullptr, *ds = nullptr;
     const size_t tokens = static_cast<size_t>(e->n_pages) * e->page;
+    const size_t slots = static_cast<size_t>(desc->max_seqs);
     bool ok = true;
-    if (L.mixer_kind == KLLM_SEQ_MIXER_ATTENTION) {
-      const kllm_seq_attention& a = L.attn;
-      ok = cudaMalloc(&k, tokens * a.kv_heads * a.dim * es) == cudaSuccess &&
-           cudaMalloc(&v, tokens * a.kv_heads * a.vdim * es) == cudaSuccess;
-    } else if (L.mixer_kind == KLLM_SEQ_MIXER_LATENT) {
-      ok = cudaMalloc(&k, tokens * (L.latent.kv_rank + L.latent.rot_dim) * es) == cudaSuccess;
-    } else {
-      const size_t n = static_cast<size_t>(desc->max_seqs) * L.linear.heads * L.linear.dim * L.linear.vdim;
-      ok = cudaMalloc(&ls, n * sizeof(float)) == cudaSuccess;
+    auto f32 = [&](float** p, size_t n) { return n == 0 || cudaMalloc(p, n * sizeof(float)) == cudaSuccess; };
+    for (int kind : {L.mixer_kind, L.mixer2_kind}) {
+      if (!ok) break;
+      if (kind == KLLM_SEQ_MIXER_ATTENTION) {
+        const kllm_seq_attention& a = L.attn;
+        ok = cudaMalloc(&k, tokens * a.kv_heads * a.dim * es) == cudaSuccess &&
+             cudaMalloc(&v, tokens * a.kv_heads * a.vdim * es) == cudaSuccess &&
+             f32(&ac, a.conv_taps > 1 ? slots * (a.conv_taps - 1) * (a.heads + a.kv_heads) * a.dim : 0);
+      } else if (kind == KLLM_SEQ_MIXER_LATENT) {
+        ok = cudaMalloc(&k, tokens * (L.latent.kv_rank + L.latent.rot_dim) * es) == cudaSuccess;
+      } else if (kind == KLLM_SEQ_MIXER_LINEAR) {
+        ok = f32(&ls, slots * L.linear.heads * L.linear.dim * L.linear.vdim);
+      } else if (kind == KLLM_SEQ_MIXER_SSM) {
+        ok = f32(&sc, slots * (L.ssm.conv_taps - 1) * L.ssm.inner) && f32(&ss, slots * L.ssm.inner * L.ssm.state);
+      } else if (kind == KLLM_SEQ_MIXER_DELTA) {
+        const kllm_seq_delta& a = L.delta;
+        ok = f32(&dc, slots * (a.conv_taps - 1) * (2 * a.kv_heads * a.dim + a.heads * a.vdim)) &&
+             f32(&ds, slots * a.heads * a.dim * a.vdim);
+      }
     }
     if (ok && L.shift) ok = cudaMalloc(&sh, static_cast<size_t>(desc->max_seqs) * desc->width * sizeof(float)) == cudaSuccess;
     e->k_pool.push_back(k);
     e->v_pool.push_back(v);
     e->shift_state.push_back(sh);
     e->linear_state.push_back(ls);
+    e->attn_conv.push_back(ac), e->ssm_conv.push_back(sc), e->ssm_state.push_back(ss);
+    e->delta_conv.push_back(dc), e->delta_state.push_back(ds);
     if (!ok) {
       delete e;
       return static_cast<int>(cudaErrorMemoryAllocation);
@@ -289,29 +346,46 @@ extern "C" int kllm_seq_create(const kllm_seq_desc* desc, void* stream, kllm_seq
   cudaMemset(e->table_dev, 0, e->table_host.size() * sizeof(int32_t));
   for (const kllm_seq_layer& L : e->layers) {
     e->any_shift = e->any_shift || L.shift != nullptr;
-    if (L.mixer_kind == KLLM_SEQ_MIXER_ATTENTION) {
-      const kllm_seq_attention& a = L.attn;
-      e->max_proj = std::max(e->max_proj, a.heads * a.dim + a.kv_heads * (a.dim + a.vdim) + (a.gate ? a.heads : 0));
-      e->max_q = std::max(e->max_q, a.heads * a.dim);
-      e->max_att = std::max(e->max_att, a.heads * a.vdim);
-      e->max_heads = std::max(e->max_heads, a.heads);
-    } else if (L.mixer_kind == KLLM_SEQ_MIXER_LATENT) {
-      const kllm_seq_latent& a = L.latent;
-      e->max_proj = std::max(e->max_proj, a.q_rank + a.kv_rank + a.rot_dim + a.heads);
-      e->max_q = std::max(e->max_q, a.q_rank);
-      e->max_qf = std::max(e->max_qf, a.heads * (a.dim + a.rot_dim));
-      e->max_qa = std::max(e->max_qa, a.heads * (a.kv_rank + a.rot_dim));
-      e->max_ol = std::max(e->max_ol, a.heads * a.kv_rank);
-      e->max_att = std::max(e->max_att, a.heads * a.vdim);
-      e->max_heads = std::max(e->max_heads, a.heads);
-    } else {
-      const kllm_seq_linear& a = L.linear;
-      e->max_proj = std::max(e->max_proj, 2 * a.heads * (a.dim + a.vdim));
-      e->max_ol = std::max(e->max_ol, a.heads * a.vdim);
-      e->max_att = std::max(e->max_att, a.heads * a.vdim);
+    e->any_mixer2 = e->any_mixer2 || L.mixer2_kind != 0;
+    e->any_parallel_ff = e->any_parallel_ff || L.parallel_ff != 0;
+    for (int kind : {L.mixer_kind, L.mixer2_kind}) {
+      if (kind == KLLM_SEQ_MIXER_ATTENTION) {
+        const kllm_seq_attention& a = L.attn;
+        e->max_proj = std::max(e->max_proj, a.heads * a.dim + a.kv_heads * (a.dim + (a.values_are_keys ? 0 : a.vdim)) +
+                                                (a.gate ? a.heads : 0));
+        e->max_q = std::max(e->max_q, a.heads * a.dim);
+        e->max_att = std::max(e->max_att, a.heads * a.vdim);
+        e->max_heads = std::max(e->max_heads, a.heads);
+      } else if (kind == KLLM_SEQ_MIXER_LATENT) {
+        const kllm_seq_latent& a = L.latent;
+        e->max_proj = std::max(e->max_proj, a.q_rank + a.kv_rank + a.rot_dim + a.heads);
+        e->max_q = std::max(e->max_q, a.q_rank);
+        e->max_qf = std::max(e->max_qf, a.heads * (a.dim + a.rot_dim));
+        e->max_qa = std::max(e->max_qa, a.heads * (a.kv_rank + a.rot_dim));
+        e->max_ol = std::max(e->max_ol, a.heads * a.kv_rank);
+        e->max_att = std::max(e->max_att, a.heads * a.vdim);
+        e->max_heads = std::max(e->max_heads, a.heads);
+      } else if (kind == KLLM_SEQ_MIXER_LINEAR) {
+        const kllm_seq_linear& a = L.linear;
+        e->max_proj = std::max(e->max_proj, 2 * a.heads * (a.dim + a.vdim));
+        e->max_ol = std::max(e->max_ol, a.heads * a.vdim);
+        e->max_att = std::max(e->max_att, a.heads * a.vdim);
+      } else if (kind == KLLM_SEQ_MIXER_SSM) {
+        const kllm_seq_ssm& a = L.ssm;
+        e->max_proj = std::max(e->max_proj, 2 * a.inner);
+        e->max_att = std::max(e->max_att, a.inner);
+        e->max_rec_a = std::max(e->max_rec_a, a.inner);
+        e->max_rec_b = std::max(e->max_rec_b, a.dt_rank + 2 * a.state);
+      } else if (kind == KLLM_SEQ_MIXER_DELTA) {
+        const kllm_seq_delta& a = L.delta;
+        e->max_proj = std::max(e->max_proj, 2 * a.kv_heads * a.dim + a.heads * a.vdim + a.heads + a.decay_rank + a.gate_rank);
+        e->max_att = std::max(e->max_att, a.heads * a.vdim);
+        e->max_rec_a = std::max(e->max_rec_a, delta_prep_row(a));
+        e->max_rec_b = std::max(e->max_rec_b, a.heads * a.vdim);
+      }
     }
     if (L.ff_kind == KLLM_SEQ_FF_DENSE) {
-      e->max_proj = std::max(e->max_proj, L.dense.ff);
+      e->max_proj = std::max(e->max_proj, (L.dense.act == KLLM_SEQ_ACT_RELU_GATE ? 2 : 1) * L.dense.ff);
       e->max_att = std::max(e->max_att, L.dense.ff);
     }
     if (L.ff_kind == KLLM_SEQ_FF_MOE) {
@@ -489,16 +563,21 @@ extern "C" int kllm_seq_step(kllm_seq_engine* e, int32_t n_entries, const int32_
   if (e->max_qf > 0) RC(e->qf.reserve(Ts * e->max_qf * 4));
   if (e->max_qa > 0) RC(e->qa.reserve(Ts * e->max_qa * 4));
   if (e->max_ol > 0) RC(e->ol.reserve(Ts * e->max_ol * 4));
+  if (e->any_mixer2) RC(e->y3.reserve(Ts * W * 4));
+  if (e->any_parallel_ff) RC(e->y4.reserve(Ts * W * 4));
+  if (e->max_rec_a > 0) RC(e->rec_a.reserve(Ts * e->max_rec_a * 4));
+  if (e->max_rec_b > 0) RC(e->rec_b.reserve(Ts * e->max_rec_b * 4));
   size_t ws_bytes = 0;
-  for (const kllm_seq_layer& L : e->layers) {
-    AttnShape a{};
-    if (L.mixer_kind == KLLM_SEQ_MIXER_ATTENTION) a.heads = L.attn.heads, a.vdim = L.attn.vdim;
-    else if (L.mixer_kind == KLLM_SEQ_MIXER_LATENT) a.heads = L.latent.heads, a.vdim = L.latent.kv_rank;
-    else continue;
-    ws_bytes = std::max(ws_bytes, attention_workspace_bytes(a, T, splits));
-  }
+  for (const kllm_seq_layer& L : e->layers)
+    for (int kind : {L.mixer_kind, L.mixer2_kind}) {
+      AttnShape a{};
+      if (kind == KLLM_SEQ_MIXER_ATTENTION) a.heads = L.attn.heads, a.vdim = L.attn.vdim;
+      else if (kind == KLLM_SEQ_MIXER_LATENT) a.heads = L.latent.heads, a.vdim = L.latent.kv_rank;
+      else continue;
+      ws_bytes = std::max(ws_bytes, attention_workspace_bytes(a, T, splits));
+    }
   for (const kllm_seq_layer& L : e->layers)  // the chunk sums of linear attention share the attention workspace
-    if (L.mixer_kind == KLLM_SEQ_MIXER_LINEAR)
+    if (L.mixer_kind == KLLM_SEQ_MIXER_LINEAR || L.mixer2_kind == KLLM_SEQ_MIXER_LINEAR)
       ws_bytes = std::max(ws_bytes, linear_attention_scratch_bytes(L.linear.heads, L.linear.dim, L.linear.vdim, T, n_entries, max_count));
   RC(e->ws.reserve(ws_bytes));
   const bool grouped = T >= kGroupedMinTokens;
@@ -518,6 +597,9 @@ extern "C" int kllm_seq_step(kllm_seq_engine* e, int32_t n_entries, const int32_
   float* proj = static_cast<float*>(e->proj.p);
   float* y = static_cast<float*>(e->y.p);
   float* y2 = static_cast<float*>(e->y2.p);
+  float* y3 = static_cast<float*>(e->y3.p);
+  float* y4 = static_cast<float*>(e->y4.p);
+  const StepRows step_rows{d_seq, d_pos, d_first, d_count, d_pos0, n_entries};
   const bool tracing = e->trace_host != nullptr;
   bool single = true;  // every entry brings one token: a row's CTA owns its sequence's state
   bool fresh_prompt = getenv("KLLM_SEQ_LATENT_EXPAND") == nullptr || getenv("KLLM_SEQ_LATENT_EXPAND")[0] != '0';
@@ -532,11 +614,17 @@ extern "C" int kllm_seq_step(kllm_seq_engine* e, int32_t n_entries, const int32_
   e->mark(-1);
   auto run_device = [&]() -> int {
   RC(launch_embed(dtype, d.embed, d_tok, x, e->any_run_embed ? static_cast<float*>(e->x0.p) : nullptr, nw(d.embed_norm),
-                  d.norm_eps, T, W, st));
+                  d.norm_eps, d.embed_scale, T, W, st));
   e->mark(KLLM_SEQ_PHASE_NORM);
   // What comes ahead of run r's mixer rides on one norm kernel (`a` may already carry the end of the run before):
   // the embedding output and the run's vector are added, the pre-norm is taken, and the token shift is applied -- inside
   // the kernel when every entry is one token, else by a kernel of its own on the fp32 rows.
+  auto router_args = [&](const kllm_seq_moe& M) {
+    return RouterArgs{M.w_router, M.shared_ff > 0 ? M.w_shared_gate : nullptr, M.experts, M.top,
+                      M.router_scale != 0.f ? M.router_scale : 1.0f, static_cast<int32_t*>(e->top_idx.p),
+                      static_cast<float*>(e->top_w.p), static_cast<float*>(e->sgate.p), M.router_kind, M.correction,
+                      M.groups, M.groups_keep, M.router_bias};
+  };
   auto launch_pre = [&](ResidNormArgs a, int r, int phase) -> int {
     const kllm_seq_layer& L = e->layers[e->run_layer[r]];
     a.x = x, a.T = T, a.width = W, a.dtype = dtype, a.eps = d.norm_eps;
@@ -546,6 +634,7 @@ extern "C" int kllm_seq_step(kllm_seq_engine* e, int32_t n_entries, const int32_
     const bool shift_after = L.shift != nullptr && !single;
     if (L.shift != nullptr && single) a.shift = ShiftArgs{L.shift, e->shift_state[r], d_seq, d_pos};
     if (shift_after) a.out_f32 = static_cast<float*>(e->hn.p);
+    if (L.parallel_ff && L.ff_kind == KLLM_SEQ_FF_MOE) a.router = router_args(L.moe);  // the experts read this row too
     RC(launch_resid_norm(a, st));
     if (shift_after)
       RC(launch_token_shift(dtype, static_cast<const float*>(e->hn.p), L.shift, e->shift_state[r], d_seq, d_pos, d_first,
@@ -553,30 +642,33 @@ extern "C" int kllm_seq_step(kllm_seq_engine* e, int32_t n_entries, const int32_
     e->mark(phase);
     return 0;
   };
-  bool pre_done = false;  // the previous run's last kernel already produced this run's h
-  for (int r = 0; r < d.n_runs; ++r) {
-    const kllm_seq_layer& L = e->layers[e->run_layer[r]];
-    if (!pre_done) RC(launch_pre(ResidNormArgs{}, r, KLLM_SEQ_PHASE_NORM));
-    pre_done = false;
-    if (L.mixer_kind == KLLM_SEQ_MIXER_ATTENTION) {
+  // one mixer of layer L (run r): reads the normed rows in e->h, writes its output rows to `yout`
+  auto run_mixer = [&](const kllm_seq_layer& L, int kind, int r, float* yout) -> int {
+    if (kind == KLLM_SEQ_MIXER_ATTENTION) {
       const kllm_seq_attention& A = L.attn;
       const AttnShape shape{A.heads, A.kv_heads, A.dim, A.vdim, A.scale, A.temp_coef, A.temp_every, A.qk_norm, A.gate,
-                            0, nullptr, 0, 0, 0};
+                            A.window, A.sink, 0, 0, 0, A.keep_first, A.softcap};
       const PagedKV kv{e->k_pool[r], e->v_pool[r], e->table_dev, e->table_stride, e->page, A.kv_heads * A.dim,
                        A.kv_heads * A.vdim};
-      const int n_proj = A.heads * A.dim + A.kv_heads * (A.dim + A.vdim) + (A.gate ? A.heads : 0);
+      const int n_proj = A.heads * A.dim + A.kv_heads * (A.dim + (A.values_are_keys ? 0 : A.vdim)) + (A.gate ? A.heads : 0);
       RC(gemm(dtype, e->h.p, A.w_in, proj, T, W, n_proj, st));
       e->mark(KLLM_SEQ_PHASE_IN_PROJ);
-      RC(launch_qk_prepare(dtype, shape, proj, A.q_norm_w, A.k_norm_w, d.norm_eps, d_seq, d_pos, e->q.p,
-                           static_cast<float*>(e->gates.p), kv, T, st));
+      if (A.values_are_keys) {
+        const AttnPrep prep{std::max(1, A.conv_taps), A.conv_w, e->attn_conv[r], A.in_bias, A.rope_dims, A.rope_pairing,
+                            A.rope_base};
+        RC(launch_qk_conv_prepare(dtype, shape, prep, proj, step_rows, e->q.p, kv, T, st));
+      } else {
+        RC(launch_qk_prepare(dtype, shape, proj, A.q_norm_w, A.k_norm_w, d.norm_eps, d_seq, d_pos, e->q.p,
+                             static_cast<float*>(e->gates.p), kv, T, st));
+      }
       e->mark(KLLM_SEQ_PHASE_QK_PREPARE);
       RC(launch_attention(dtype, shape, e->q.p, static_cast<const float*>(e->gates.p), kv, n_entries, d_first, d_count,
-                          d_eseq, d_pos0, max_count, max_ctx, splits, static_cast<float*>(e->ws.p), e->att.p, T, d_seq,
-                          d_pos, st));
+                          d_eseq, d_pos0, max_count, max_ctx, window_splits(A.keep_first > 0 ? 0 : A.window),
+                          static_cast<float*>(e->ws.p), e->att.p, T, d_seq, d_pos, st));
       e->mark(KLLM_SEQ_PHASE_ATTENTION);
-      RC(gemm(dtype, e->att.p, A.w_out, y, T, A.heads * A.vdim, W, st));
+      RC(gemm(dtype, e->att.p, A.w_out, yout, T, A.heads * A.vdim, W, st));
       e->mark(KLLM_SEQ_PHASE_OUT_PROJ);
-    } else if (L.mixer_kind == KLLM_SEQ_MIXER_LATENT) {
+    } else if (kind == KLLM_SEQ_MIXER_LATENT) {
       const kllm_seq_latent& A = L.latent;
       const LatentShape ls{A.heads, A.dim, A.rot_dim, A.vdim, A.q_rank, A.kv_rank, A.rope_dims, A.rope_base};
       const int krow = A.kv_rank + A.rot_dim;
@@ -610,7 +702,7 @@ extern "C" int kllm_seq_step(kllm_seq_engine* e, int32_t n_entries, const int32_
         RC(launch_attention(dtype, eshape, e->lat_q.p, gates, rows, n_entries, d_first, d_count, d_eseq, d_pos0, max_count,
                             max_ctx, 1, static_cast<float*>(e->ws.p), e->att.p, T, d_seq, d_pos, st));
         e->mark(KLLM_SEQ_PHASE_ATTENTION);
-        RC(gemm(dtype, e->att.p, A.w_out, y, T, A.heads * A.vdim, W, st));
+        RC(gemm(dtype, e->att.p, A.w_out, yout, T, A.heads * A.vdim, W, st));
         e->mark(KLLM_SEQ_PHASE_OUT_PROJ);
       } else {
       RC(launch_latent_prepare(dtype, ls, proj, A.q_norm_w, A.kv_norm_w, d.norm_eps, d_seq, d_pos, e->q.p, gates, kv, nullptr,
@@ -631,10 +723,10 @@ extern "C" int kllm_seq_step(kllm_seq_engine* e, int32_t n_entries, const int32_
       else
         RC(launch_latent_expand(dtype, ls, static_cast<const float*>(e->ol.p), A.w_uv, e->att.p, T, st));
       e->mark(KLLM_SEQ_PHASE_ATTENTION);
-      RC(gemm(dtype, e->att.p, A.w_out, y, T, A.heads * A.vdim, W, st));
+      RC(gemm(dtype, e->att.p, A.w_out, yout, T, A.heads * A.vdim, W, st));
       e->mark(KLLM_SEQ_PHASE_OUT_PROJ);
       }
-    } else {
+    } else if (kind == KLLM_SEQ_MIXER_LINEAR) {
       const kllm_seq_linear& A = L.linear;
       RC(gemm(dtype, e->h.p, A.w_in, proj, T, W, 2 * A.heads * (A.dim + A.vdim), st));
       e->mark(KLLM_SEQ_PHASE_IN_PROJ);
@@ -643,9 +735,123 @@ extern "C" int kllm_seq_step(kllm_seq_engine* e, int32_t n_entries, const int32_
       RC(launch_linear_out(dtype, A.heads, A.dim, A.vdim, static_cast<const float*>(e->ol.p), proj, A.out_norm_w, d.norm_eps,
                            e->att.p, T, st));
       e->mark(KLLM_SEQ_PHASE_ATTENTION);
-      RC(gemm(dtype, e->att.p, A.w_out, y, T, A.heads * A.vdim, W, st));
+      RC(gemm(dtype, e->att.p, A.w_out, yout, T, A.heads * A.vdim, W, st));
+      e->mark(KLLM_SEQ_PHASE_OUT_PROJ);
+    } else if (kind == KLLM_SEQ_MIXER_SSM) {
+      const kllm_seq_ssm& A = L.ssm;
+      float* uc = static_cast<float*>(e->rec_a.p);
+      float* low = static_cast<float*>(e->rec_b.p);
+      RC(gemm(dtype, e->h.p, A.w_in, proj, T, W, 2 * A.inner, st));
+      e->mark(KLLM_SEQ_PHASE_IN_PROJ);
+      RC(launch_ssm_conv(dtype, A, proj, e->ssm_conv[r], step_rows, uc, e->att.p, T, st));
+      RC(gemm(dtype, e->att.p, A.w_x, low, T, A.inner, A.dt_rank + 2 * A.state, st));
+      e->mark(KLLM_SEQ_PHASE_QK_PREPARE);
+      RC(launch_ssm_scan(dtype, A, proj, uc, low, e->ssm_state[r], step_rows, d_eseq, max_count, e->att.p, st));
+      e->mark(KLLM_SEQ_PHASE_ATTENTION);
+      RC(gemm(dtype, e->att.p, A.w_out, yout, T, A.inner, W, st));
+      e->mark(KLLM_SEQ_PHASE_OUT_PROJ);
+    } else {
+      const kllm_seq_delta& A = L.delta;
+      float* prep = static_cast<float*>(e->rec_a.p);
+      float* o = static_cast<float*>(e->rec_b.p);
+      const int n_proj = 2 * A.kv_heads * A.dim + A.heads * A.vdim + A.heads + A.decay_rank + A.gate_rank;
+      RC(gemm(dtype, e->h.p, A.w_in, proj, T, W, n_proj, st));
+      e->mark(KLLM_SEQ_PHASE_IN_PROJ);
+      RC(launch_delta_prepare(A, proj, e->delta_conv[r], step_rows, prep, T, st));
+      e->mark(KLLM_SEQ_PHASE_QK_PREPARE);
+      RC(launch_delta_rule(A, prep, e->delta_state[r], step_rows, d_eseq, max_count, o, st));
+      RC(launch_delta_out(dtype, A, o, prep, d.norm_eps, e->att.p, T, st));
+      e->mark(KLLM_SEQ_PHASE_ATTENTION);
+      RC(gemm(dtype, e->att.p, A.w_out, yout, T, A.heads * A.vdim, W, st));
       e->mark(KLLM_SEQ_PHASE_OUT_PROJ);
     }
+    return 0;
+  };
+  // the feed-forward of layer L on the rows in e->h: its output goes to `yout`, a shared expert's (when it did not ride
+  // along with the routed ones) to y2 with *shared_out set; the router has already run
+  auto run_ff = [&](const kllm_seq_layer& L, float* yout, bool* shared_out) -> int {
+    *shared_out = false;
+    if (L.ff_kind == KLLM_SEQ_FF_DENSE) {
+      const kllm_seq_dense& F = L.dense;
+      if (F.act == KLLM_SEQ_ACT_RELU_GATE) {
+        RC(gemm(dtype, e->h.p, F.up, proj, T, W, 2 * F.ff, st));
+        RC(launch_gated_act(dtype, GatedAct{F.act, 0.f, 0.f}, proj, e->att.p, T, F.ff, st));
+      } else {
+        RC(gemm(dtype, e->h.p, F.up, proj, T, W, F.ff, st));
+        RC(launch_activation(dtype, F.act, F.act_a, F.act_b, proj, e->att.p, Ts * F.ff, st));
+      }
+      RC(gemm(dtype, e->att.p, F.down, yout, T, F.ff, W, st));
+      e->mark(KLLM_SEQ_PHASE_EXPERTS);
+      return 0;
+    }
+    const kllm_seq_moe& M = L.moe;
+    int32_t* top_idx = static_cast<int32_t*>(e->top_idx.p);
+    float* top_w = static_cast<float*>(e->top_w.p);
+    float* sgate = static_cast<float*>(e->sgate.p);
+    const GatedAct act{M.act, M.act_limit, M.act_alpha};
+    bool shared_done = false;  // the shared expert went through the pair kernels: yout already holds its part
+    if (!grouped) {
+      SharedExpert sh{};
+      // every pair streams its expert's weights once: beyond a few tokens the shared expert is cheaper as a product
+      if (M.shared_ff > 0 && T <= kSharedRideTokens && shared_expert_rides_along(M.top, M.ff, M.shared_ff)) {
+        sh = SharedExpert{M.shared_gate_up, M.shared_down, M.w_shared_gate ? sgate : nullptr, e->att.p, M.shared_ff,
+                          M.shared_act_limit};
+        shared_done = true;
+      }
+      RC(launch_expert_gate_up(dtype, e->h.p, M.gate_up, top_idx, e->inter.p, T, M.top, M.ff, W, sh, act, st));
+      RC(launch_expert_down(dtype, e->inter.p, M.down, top_idx, top_w, yout, T, M.top, M.ff, W, sh, st));
+    } else {
+      const int n_pairs = T * M.top;
+      const int cap = ((n_pairs + kGroupBlock - 1) / kGroupBlock + M.experts) * kGroupBlock;
+      const int n_blocks = cap / kGroupBlock;
+      RC(e->sort.reserve((static_cast<size_t>(M.experts) + 1 + cap + n_blocks) * 4));
+      int32_t* counts_d = static_cast<int32_t*>(e->sort.p);
+      int32_t* sorted = counts_d + M.experts + 1;
+      int32_t* block_expert = sorted + cap;
+      RC(launch_sort_pairs(top_idx, n_pairs, M.experts, kGroupBlock, counts_d, sorted, block_expert, cap, st));
+      GroupedArgs g{};
+      g.sorted_pair = sorted, g.block_expert = block_expert, g.n_blocks = n_blocks, g.block = kGroupBlock;
+      g.experts = M.experts, g.act = act;
+      const int inner_epilogue = M.act == KLLM_SEQ_ACT_RELU2 ? 2 : 1;
+      if (grouped_tensor_core_usable(dtype, W, M.ff)) {
+        // rows in sorted order: a gathered copy of h, the expert's inner activations, then scattered back by pair
+        RC(e->sorted_a.reserve(static_cast<size_t>(cap) * W * es));
+        RC(e->sorted_inter.reserve(static_cast<size_t>(cap) * M.ff * es));
+        RC(gather_rows_bf16(e->h.p, sorted, M.top, e->sorted_a.p, cap, W, st));
+        g.sorted_layout = 1;
+        g.a = e->sorted_a.p, g.w = M.gate_up, g.K = W, g.N = M.ff, g.epilogue = inner_epilogue, g.out = e->sorted_inter.p;
+        RC(gemm_grouped(dtype, g, st));
+        g.a = e->sorted_inter.p, g.w = M.down, g.K = M.ff, g.N = W, g.epilogue = 0, g.out = e->pairs_out.p;
+        RC(gemm_grouped(dtype, g, st));
+      } else {
+        g.a = e->h.p, g.w = M.gate_up, g.a_row_div = M.top, g.K = W, g.N = M.ff, g.epilogue = inner_epilogue, g.out = e->inter.p;
+        RC(gemm_grouped(dtype, g, st));
+        g.a = e->inter.p, g.w = M.down, g.a_row_div = 1, g.K = M.ff, g.N = W, g.epilogue = 0, g.out = e->pairs_out.p;
+        RC(gemm_grouped(dtype, g, st));
+      }
+      RC(launch_combine_pairs(static_cast<const float*>(e->pairs_out.p), top_w, yout, T, M.top, W, st));
+    }
+    e->mark(KLLM_SEQ_PHASE_EXPERTS);
+    if (M.shared_ff > 0 && !shared_done) {
+      RC(gemm(dtype, e->h.p, M.shared_gate_up, proj, T, W, 2 * M.shared_ff, st));
+      RC(launch_gated_act(dtype, GatedAct{M.act, M.shared_act_limit, M.act_alpha}, proj, e->att.p, T, M.shared_ff, st));
+      RC(gemm(dtype, e->att.p, M.shared_down, y2, T, M.shared_ff, W, st));
+      e->mark(KLLM_SEQ_PHASE_SHARED);
+      *shared_out = true;
+    }
+    return 0;
+  };
+  bool pre_done = false;  // the previous run's last kernel already produced this run's h
+  for (int r = 0; r < d.n_runs; ++r) {
+    const kllm_seq_layer& L = e->layers[e->run_layer[r]];
+    if (!pre_done) RC(launch_pre(ResidNormArgs{}, r, KLLM_SEQ_PHASE_NORM));
+    pre_done = false;
+    RC(run_mixer(L, L.mixer_kind, r, y));
+    if (L.mixer2_kind != 0) RC(run_mixer(L, L.mixer2_kind, r, y3));
+    // what the mixers add to x: c1 y (+ c3 y3)
+    ResidNormArgs mixed{};
+    mixed.y1 = y, mixed.y1_scale = L.mixer_scale;
+    if (L.mixer2_kind != 0) mixed.y3 = y3, mixed.y3_scale = L.mixer2_scale;
 
     // what follows this layer run: the next run's additions and pre-norm can ride on this run's last kernel
     const bool fuse_next = r + 1 < d.n_runs && !tracing;
@@ -659,89 +865,29 @@ extern "C" int kllm_seq_step(kllm_seq_engine* e, int32_t n_entries, const int32_
       e->mark(KLLM_SEQ_PHASE_NORM);
       return 0;
     };
+    const kllm_seq_moe& M = L.moe;
+    const float* sgate = static_cast<const float*>(e->sgate.p);
     if (L.ff_kind == KLLM_SEQ_FF_NONE) {
-      ResidNormArgs a{};
-      a.y1 = y, a.post = nw(L.post_mixer);
-      RC(end_of_run(a));
-    } else if (L.ff_kind == KLLM_SEQ_FF_DENSE) {
-      const kllm_seq_dense& F = L.dense;
-      {
-        ResidNormArgs a{};
-        a.x = x, a.y1 = y, a.post = nw(L.post_mixer), a.pre = nw(L.pre_ff), a.out = e->h.p, a.T = T, a.width = W;
-        a.dtype = dtype, a.eps = d.norm_eps;
-        RC(launch_resid_norm(a, st));
-        e->mark(KLLM_SEQ_PHASE_ROUTER);
-      }
-      RC(gemm(dtype, e->h.p, F.up, proj, T, W, F.ff, st));
-      RC(launch_activation(dtype, F.act, F.act_a, F.act_b, proj, e->att.p, Ts * F.ff, st));
-      RC(gemm(dtype, e->att.p, F.down, y, T, F.ff, W, st));
-      e->mark(KLLM_SEQ_PHASE_EXPERTS);
-      ResidNormArgs a{};
-      a.y1 = y, a.post = nw(L.post_ff);
-      RC(end_of_run(a));
+      mixed.post = nw(L.post_mixer);
+      RC(end_of_run(mixed));
+    } else if (L.parallel_ff) {
+      // the feed-forward read the same rows as the mixers (the pre-norm kernel also routed them): one sum joins x
+      bool shared = false;
+      RC(run_ff(L, y4, &shared));
+      mixed.y4 = y4;
+      if (shared) mixed.y2 = y2, mixed.s2 = M.w_shared_gate ? sgate : nullptr;
+      RC(end_of_run(mixed));
     } else {
-      const kllm_seq_moe& M = L.moe;
-      int32_t* top_idx = static_cast<int32_t*>(e->top_idx.p);
-      float* top_w = static_cast<float*>(e->top_w.p);
-      float* sgate = static_cast<float*>(e->sgate.p);
-      {  // the norm kernel that writes the experts' input also routes its row
-        ResidNormArgs a{};
-        a.x = x, a.y1 = y, a.post = nw(L.post_mixer), a.pre = nw(L.pre_ff), a.out = e->h.p, a.T = T, a.width = W;
+      {  // the norm kernel that writes the feed-forward's input also routes its row
+        ResidNormArgs a = mixed;
+        a.x = x, a.post = nw(L.post_mixer), a.pre = nw(L.pre_ff), a.out = e->h.p, a.T = T, a.width = W;
         a.dtype = dtype, a.eps = d.norm_eps;
-        a.router = RouterArgs{M.w_router, M.shared_ff > 0 ? M.w_shared_gate : nullptr, M.experts, M.top, M.router_scale,
-                              top_idx, top_w, sgate, M.router_kind, M.correction, M.groups, M.groups_keep};
+        if (L.ff_kind == KLLM_SEQ_FF_MOE) a.router = router_args(M);
         RC(launch_resid_norm(a, st));
         e->mark(KLLM_SEQ_PHASE_ROUTER);
       }
-      bool shared_done = false;  // the shared expert went through the pair kernels: y already holds its part
-      if (!grouped) {
-        SharedExpert sh{};
-        // every pair streams its expert's weights once: beyond a few tokens the shared expert is cheaper as a product
-        if (M.shared_ff > 0 && T <= kSharedRideTokens && shared_expert_rides_along(M.top, M.ff, M.shared_ff)) {
-          sh = SharedExpert{M.shared_gate_up, M.shared_down, M.w_shared_gate ? sgate : nullptr, e->att.p, M.shared_ff};
-          shared_done = true;
-        }
-        RC(launch_expert_gate_up(dtype, e->h.p, M.gate_up, top_idx, e->inter.p, T, M.top, M.ff, W, sh, M.act, st));
-        RC(launch_expert_down(dtype, e->inter.p, M.down, top_idx, top_w, y, T, M.top, M.ff, W, sh, st));
-      } else {
-        const int n_pairs = T * M.top;
-        const int cap = ((n_pairs + kGroupBlock - 1) / kGroupBlock + M.experts) * kGroupBlock;
-        const int n_blocks = cap / kGroupBlock;
-        RC(e->sort.reserve((static_cast<size_t>(M.experts) + 1 + cap + n_blocks) * 4));
-        int32_t* counts_d = static_cast<int32_t*>(e->sort.p);
-        int32_t* sorted = counts_d + M.experts + 1;
-        int32_t* block_expert = sorted + cap;
-        RC(launch_sort_pairs(top_idx, n_pairs, M.experts, kGroupBlock, counts_d, sorted, block_expert, cap, st));
-        GroupedArgs g{};
-        g.sorted_pair = sorted, g.block_expert = block_expert, g.n_blocks = n_blocks, g.block = kGroupBlock;
-        g.experts = M.experts;
-        const int inner_epilogue = M.act == KLLM_SEQ_ACT_RELU2 ? 2 : 1;
-        if (grouped_tensor_core_usable(dtype, W, M.ff)) {
-          // rows in sorted order: a gathered copy of h, the expert's inner activations, then scattered back by pair
-          RC(e->sorted_a.reserve(static_cast<size_t>(cap) * W * es));
-          RC(e->sorted_inter.reserve(static_cast<size_t>(cap) * M.ff * es));
-          RC(gather_rows_bf16(e->h.p, sorted, M.top, e->sorted_a.p, cap, W, st));
-          g.sorted_layout = 1;
-          g.a = e->sorted_a.p, g.w = M.gate_up, g.K = W, g.N = M.ff, g.epilogue = inner_epilogue, g.out = e->sorted_inter.p;
-          RC(gemm_grouped(dtype, g, st));
-          g.a = e->sorted_inter.p, g.w = M.down, g.K = M.ff, g.N = W, g.epilogue = 0, g.out = e->pairs_out.p;
-          RC(gemm_grouped(dtype, g, st));
-        } else {
-          g.a = e->h.p, g.w = M.gate_up, g.a_row_div = M.top, g.K = W, g.N = M.ff, g.epilogue = inner_epilogue, g.out = e->inter.p;
-          RC(gemm_grouped(dtype, g, st));
-          g.a = e->inter.p, g.w = M.down, g.a_row_div = 1, g.K = M.ff, g.N = W, g.epilogue = 0, g.out = e->pairs_out.p;
-          RC(gemm_grouped(dtype, g, st));
-        }
-        RC(launch_combine_pairs(static_cast<const float*>(e->pairs_out.p), top_w, y, T, M.top, W, st));
-      }
-      e->mark(KLLM_SEQ_PHASE_EXPERTS);
-      const bool shared = M.shared_ff > 0 && !shared_done;
-      if (shared) {
-        RC(gemm(dtype, e->h.p, M.shared_gate_up, proj, T, W, 2 * M.shared_ff, st));
-        RC(launch_silu_mul(dtype, proj, e->att.p, T, M.shared_ff, st));
-        RC(gemm(dtype, e->att.p, M.shared_down, y2, T, M.shared_ff, W, st));
-        e->mark(KLLM_SEQ_PHASE_SHARED);
-      }
+      bool shared = false;
+      RC(run_ff(L, y, &shared));
       ResidNormArgs a{};
       a.y1 = y, a.y2 = shared ? y2 : nullptr, a.s2 = shared && M.w_shared_gate ? sgate : nullptr;
       a.post = nw(L.post_ff);
@@ -759,8 +905,8 @@ extern "C" int kllm_seq_step(kllm_seq_engine* e, int32_t n_entries, const int32_
     RC(launch_resid_norm(a, st));
     float* lg = static_cast<float*>(e->logits.p);
     RC(gemm(dtype, e->hw.p, d.head, lg, n_want, W, d.vocab, st));
-    if (d.logit_scale != 0.f && d.logit_scale != 1.f)
-      RC(launch_scale(lg, d.logit_scale, static_cast<size_t>(n_want) * d.vocab, st));
+    if ((d.logit_scale != 0.f && d.logit_scale != 1.f) || d.logit_softcap > 0.f)
+      RC(launch_scale(lg, d.logit_scale, d.logit_softcap, static_cast<size_t>(n_want) * d.vocab, st));
     if (argmax_host) RC(launch_argmax_rows(lg, static_cast<int32_t*>(e->amax.p), n_want, d.vocab, st));
   }
   return 0;

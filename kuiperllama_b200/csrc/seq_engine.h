@@ -54,14 +54,31 @@ struct AttnShape {
   int q_f32;        // the queries are fp32 whatever the compute type
   int out_f32;      // the output is written in fp32 whatever the compute type
   int no_merge;     // leave the splits' partial results in the workspace: the caller merges them (latent_merge_expand)
+  int keep_first;   // with a window: the first keep_first positions stay visible to every later one
+  float softcap;    // score <- softcap * tanh(score / softcap) after the scale; 0: none
 };
 
-// ---- seq_kernels.cu -----------------------------------------------------------------------------------------------
-// x[t] = norm(table[tokens[t]]) (norm.w == null: the row itself); `copy` (optional) receives the same rows
-int launch_embed(int dtype, const void* table, const int32_t* tokens, float* x, float* copy, const NormW& norm, float eps,
-                 int T, int width, cudaStream_t s);
+// The activation that joins a gate row's product g and an up row's product u (see KLLM_SEQ_ACT_*).
+struct GatedAct {
+  int kind;
+  float limit, alpha;
+};
+__host__ __device__ inline float gated_act(const GatedAct& a, float g, float u) {
+  if (a.kind == KLLM_SEQ_ACT_CLAMP_SWIGLU) {
+    g = fminf(g, a.limit);
+    u = fminf(fmaxf(u, -a.limit), a.limit);
+    return g / (1.0f + expf(-a.alpha * g)) * (u + 1.0f);
+  }
+  if (a.kind == KLLM_SEQ_ACT_RELU_GATE) return fmaxf(g, 0.f) * u;
+  return g / (1.0f + expf(-g)) * u;
+}
 
-// x += N(y1 + s2[t] * y2; post) (optional; y2 optional; post.w == null: the sum itself);  x += add_rows[t];
+// ---- seq_kernels.cu -----------------------------------------------------------------------------------------------
+// x[t] = norm(table[tokens[t]] * scale) (norm.w == null: the scaled row itself); `copy` (optional) receives the same rows
+int launch_embed(int dtype, const void* table, const int32_t* tokens, float* x, float* copy, const NormW& norm, float eps,
+                 float scale, int T, int width, cudaStream_t s);
+
+// x += N(c1 y1 + s2[t] * y2 + c3 y3 + c4 y4; post) (optional; y2, y3, y4 optional; post.w == null: the sum itself);  x += add_rows[t];
 // x += add (a [width] vector, optional);  out = N(x; pre) in the compute type (optional) -- in this order.  `rows` (optional) gathers: row i reads x[rows[i]], and x is then
 // left untouched (only `out` is written).
 // Router of a mixture of experts for the rows of `out` (optional, w_router != NULL; needs `pre`): logits z = Wr h in
@@ -80,6 +97,7 @@ struct RouterArgs {
   int kind;
   const float* correction;  // [experts] or NULL
   int groups, groups_keep;
+  const float* bias;        // [experts] added to the logits, or NULL
 };
 __host__ __device__ inline size_t router_smem_floats(const RouterArgs& r) { return 2 * static_cast<size_t>(r.experts) + r.groups; }
 // Token shift on the rows a norm kernel writes, for steps in which every sequence brings ONE token: the row's CTA owns
@@ -106,6 +124,9 @@ struct ResidNormArgs {
   const float* add_rows;  // [T, width] added to x row by row (before `add`), optional
   float* out_f32;         // instead of `out`: the normed rows in fp32 (a token-shift kernel follows)
   ShiftArgs shift;        // inline token shift (single-token steps)
+  const float* y3;        // further addends of the sum that joins x (with y1)
+  const float* y4;
+  float y1_scale, y3_scale, y4_scale;  // their coefficients c1, c3, c4; 0 means 1
 };
 int launch_resid_norm(const ResidNormArgs& a, cudaStream_t s);
 
@@ -179,8 +200,8 @@ int launch_linear_out(int dtype, int heads, int dim, int vdim, const float* o, c
                       void* out, int T, cudaStream_t s);
 // out = act(z) element by element (z fp32 [n], out compute type): KLLM_SEQ_ACT_XIELU with (a, b), or KLLM_SEQ_ACT_RELU2
 int launch_activation(int dtype, int act, float a, float b, const float* z, void* out, size_t n, cudaStream_t s);
-// v *= scale
-int launch_scale(float* v, float scale, size_t n, cudaStream_t s);
+// v *= scale (0: 1), then v <- cap * tanh(v / cap) (cap 0: none)
+int launch_scale(float* v, float scale, float cap, size_t n, cudaStream_t s);
 
 // Router: z = Wr h (fp32), s = softmax(z), the `top` largest, weights s / (sum + 1e-20) * scale; shared-expert gate
 // sigmoid(w_sg . h) when w_sg is given.
@@ -198,24 +219,74 @@ struct SharedExpert {
   const float* gate;    // [T] or NULL
   void* inter;          // [T, ff] workspace in the compute type
   int ff;               // 0: no shared expert in these kernels
+  float limit;          // its own clamp when the activation has one
 };
 bool shared_expert_rides_along(int top, int ff, int shared_ff);
 // act KLLM_SEQ_ACT_RELU2: inter[pair] = max(Wu h, 0)^2 with gate_up = [experts][ff][width] (no shared expert then)
 int launch_expert_gate_up(int dtype, const void* h, const void* gate_up, const int32_t* top_idx, void* inter, int T,
-                          int top, int ff, int width, const SharedExpert& sh, int act, cudaStream_t s);
+                          int top, int ff, int width, const SharedExpert& sh, const GatedAct& act, cudaStream_t s);
 int launch_expert_down(int dtype, const void* inter, const void* down, const int32_t* top_idx, const float* top_w,
                        float* y, int T, int top, int ff, int width, const SharedExpert& sh, cudaStream_t s);
 
 // y[t] = sum_k w[t, k] * yp[t * top + k]   (fp32 [T * top, width] -> [T, width])
 int launch_combine_pairs(const float* yp, const float* top_w, float* y, int T, int top, int width, cudaStream_t s);
 
-// out[t, f] = silu(gu[t, f]) * gu[t, ff + f]   (gu fp32 [T, 2*ff], out compute type [T, ff])
-int launch_silu_mul(int dtype, const float* gu, void* out, int T, int ff, cudaStream_t s);
+// out[t, f] = act(gu[t, f], gu[t, ff + f])   (gu fp32 [T, 2*ff], out compute type [T, ff]; silu(g) * u for KLLM_SEQ_ACT_SWIGLU)
+int launch_gated_act(int dtype, const GatedAct& act, const float* gu, void* out, int T, int ff, cudaStream_t s);
 
 // Routed experts over token blocks (prefill): rows grouped by expert.  sort_pairs builds, on the device, the list of
 // pairs ordered by expert in blocks of `block` rows (padded with -1), and the expert of every block.
 int launch_sort_pairs(const int32_t* top_idx, int n_pairs, int experts, int block, int32_t* counts /*[experts+1]*/,
                       int32_t* sorted_pair /*[cap]*/, int32_t* block_expert /*[cap/block]*/, int cap, cudaStream_t s);
+
+// ---- seq_recurrent.cu: short convolutions with their state, query / key preparation behind one, selective scan, gated delta rule ----
+// Where the last taps - 1 inputs of a convolution live: [slots][taps - 1][channels] fp32, row i of a sequence of length n
+// holds the input at position n - (taps - 1) + i (positions below 0 are never read).
+// Rows of one step: row t of an entry sees the entry's earlier rows directly and the sequence's state before them.  The CTA
+// of an entry's first row also computes the entry's next taps - 2 rows (every read of the old state happens there) and then
+// writes the new state; no other CTA touches the state.
+struct StepRows {
+  const int32_t* tok_seq;
+  const int32_t* tok_pos;
+  const int32_t* ent_first;
+  const int32_t* ent_count;
+  const int32_t* ent_pos0;
+  int n_entries;
+};
+struct AttnPrep {
+  int taps;               // 1: no convolution
+  const float* conv_w;    // [(heads + kv_heads) * dim][taps]
+  float* conv_state;      // [slots][taps - 1][(heads + kv_heads) * dim]
+  const float* bias;      // [(heads + kv_heads) * dim] or NULL
+  int rope_dims, rope_pairing;
+  float rope_base;
+};
+// qk [T, heads*dim + kv_heads*dim] fp32 (projection output, values are the keys): bias, convolution, then the keys as they
+// are go to the value pages, and the rotated queries / keys to q (compute type) and the key pages.
+int launch_qk_conv_prepare(int dtype, const AttnShape& a, const AttnPrep& p, const float* qk, const StepRows& rows, void* q,
+                           const PagedKV& kv, int T, cudaStream_t s);
+
+// u [T, 2 * inner] fp32 (u | z rows of the input projection) -> uc [T, inner] fp32 and uc_ct (compute type): silu(conv(u) + b)
+int launch_ssm_conv(int dtype, const kllm_seq_ssm& m, const float* uz, float* conv_state, const StepRows& rows, float* uc,
+                    void* uc_ct, int T, cudaStream_t s);
+// the scan over every entry from its sequence's state ([slots][inner][state] fp32, zeros at position 0):
+// out[t] = y[t] * silu(z[t]) in the compute type
+int launch_ssm_scan(int dtype, const kllm_seq_ssm& m, const float* uz, const float* uc, const float* low, float* state,
+                    const StepRows& rows, const int32_t* ent_seq, int max_count, void* out, cudaStream_t s);
+
+// proj [T, 2*kv_heads*dim + heads*vdim + heads + decay_rank + gate_rank] fp32 -> prep [T, delta_prep_row()] fp32:
+// q | k (unit vectors, q scaled) | v | beta | decay [heads*dim] | gate [heads*vdim]
+__host__ __device__ inline int delta_prep_row(const kllm_seq_delta& m) {
+  return 2 * m.kv_heads * m.dim + m.heads * m.vdim + m.heads + m.heads * m.dim + m.heads * m.vdim;
+}
+int launch_delta_prepare(const kllm_seq_delta& m, const float* proj, float* conv_state, const StepRows& rows, float* prep, int T,
+                         cudaStream_t s);
+// the recurrence of every entry from its sequence's state ([slots][heads][dim][vdim] fp32); o [T, heads*vdim] fp32
+int launch_delta_rule(const kllm_seq_delta& m, const float* prep, float* state, const StepRows& rows, const int32_t* ent_seq,
+                      int max_count, float* o, cudaStream_t s);
+// out[t, h] = o[t, h] / rms(o[t, h]) * norm_w * gate[t, h] in the compute type
+int launch_delta_out(int dtype, const kllm_seq_delta& m, const float* o, const float* prep, float eps, void* out, int T,
+                     cudaStream_t s);
 
 // ---- seq_gemm.cu --------------------------------------------------------------------------------------------------
 // out[T, N] (fp32) = a[T, K] . w[N, K]^T, a and w in the compute type, fp32 accumulation.
@@ -231,9 +302,10 @@ struct GroupedArgs {
   const int32_t* block_expert;  // [n_blocks] expert or -1
   int a_row_div;            // row of `a` for pair p is p / a_row_div (gate_up: top; down: 1)
   int n_blocks, block, K, N;
-  // epilogue: 0 = out[pair, n] = acc (fp32);  1 = out[pair, f] = silu(acc_gate) * acc_up in the compute type (the
+  // epilogue: 0 = out[pair, n] = acc (fp32);  1 = out[pair, f] = gated_act(acc_gate, acc_up) in the compute type (the
   // weights hold ff gate rows, then ff up rows; N = ff);  2 = out[pair, f] = max(acc, 0)^2 in the compute type
   int epilogue;
+  GatedAct act;             // epilogue 1
   void* out;
   // tensor-core form (bf16): `a` is already in sorted order [n_blocks * block, K] and epilogue 1 writes its result in
   // sorted order too; `experts` sizes the weight map

@@ -113,7 +113,8 @@ constexpr int TM = 64, TN = 64, TK = 16;
 template <typename AT, bool GROUPED, int EPI>
 __global__ void __launch_bounds__(256)
 tiled_kernel(const AT* __restrict__ a, const AT* __restrict__ w, void* __restrict__ out_, int T, int K, int N,
-             const int32_t* __restrict__ sorted_pair, const int32_t* __restrict__ block_expert, int a_row_div) {
+             const int32_t* __restrict__ sorted_pair, const int32_t* __restrict__ block_expert, int a_row_div,
+             GatedAct act = GatedAct{KLLM_SEQ_ACT_SWIGLU, 0.f, 0.f}) {
   __shared__ float As[TK][TM + 4];
   __shared__ float Ws[EPI == 1 ? 2 : 1][TK][TN + 4];
   __shared__ int32_t rowsrc[TM], rowdst[TM];
@@ -188,7 +189,7 @@ tiled_kernel(const AT* __restrict__ a, const AT* __restrict__ w, void* __restric
       if (n >= N) continue;
       if (EPI == 1) {
         const float g = acc[0][i][j], u = acc[EPI == 1 ? 1 : 0][i][j];
-        st_t(static_cast<AT*>(out_) + static_cast<size_t>(dst) * N + n, g / (1.0f + expf(-g)) * u);
+        st_t(static_cast<AT*>(out_) + static_cast<size_t>(dst) * N + n, gated_act(act, g, u));
       } else if (EPI == 2) {
         const float u = fmaxf(acc[0][i][j], 0.f);
         st_t(static_cast<AT*>(out_) + static_cast<size_t>(dst) * N + n, u * u);
@@ -235,7 +236,7 @@ int grouped_t(const GroupedArgs& g, cudaStream_t s) {
   if (g.block != TM) return KLLM_E_INVALID;
   if (g.epilogue == 1)
     tiled_kernel<AT, true, 1><<<grid, 256, 0, s>>>(static_cast<const AT*>(g.a), static_cast<const AT*>(g.w), g.out, 0, g.K,
-                                                  g.N, g.sorted_pair, g.block_expert, g.a_row_div);
+                                                  g.N, g.sorted_pair, g.block_expert, g.a_row_div, g.act);
   else if (g.epilogue == 2)
     tiled_kernel<AT, true, 2><<<grid, 256, 0, s>>>(static_cast<const AT*>(g.a), static_cast<const AT*>(g.w), g.out, 0, g.K,
                                                   g.N, g.sorted_pair, g.block_expert, g.a_row_div);
@@ -280,7 +281,7 @@ int gemm_grouped(int dtype, const GroupedArgs& g, cudaStream_t s) {
     if (dtype != KLLM_SEQ_BF16 || g.block != umma::GBN) return KLLM_E_INVALID;
     g_umma_used = true;
     if (g.epilogue == 1)
-      return umma::launch_grouped<1>(g.a, g.w, g.out, g.sorted_pair, g.block_expert, g.n_blocks, g.experts, g.K, g.N, s);
+      return umma::launch_grouped<1>(g.a, g.w, g.out, g.sorted_pair, g.block_expert, g.n_blocks, g.experts, g.K, g.N, s, g.act);
     if (g.epilogue == 2)
       return umma::launch_grouped<2>(g.a, g.w, g.out, g.sorted_pair, g.block_expert, g.n_blocks, g.experts, g.K, g.N, s);
     return umma::launch_grouped<0>(g.a, g.w, g.out, g.sorted_pair, g.block_expert, g.n_blocks, g.experts, g.K, g.N, s);

@@ -213,7 +213,7 @@ template <int EPI>
 __global__ void __launch_bounds__(THREADS, 1)
 umma_grouped_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a,
                     void* __restrict__ out_, const int32_t* __restrict__ sorted_pair,
-                    const int32_t* __restrict__ block_expert, int N, int K) {
+                    const int32_t* __restrict__ block_expert, int N, int K, GatedAct act) {
   constexpr int NA = EPI == 1 ? 2 : 1;
   constexpr int B_BYTES = GBN * BK * 2;
   constexpr int STAGE = NA * A_BYTES + B_BYTES;
@@ -306,7 +306,7 @@ umma_grouped_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             if (EPI == 1) {
               const float g = __uint_as_float(r[j]), up = __uint_as_float(u[j]);
               static_cast<__nv_bfloat16*>(out_)[static_cast<size_t>(br) * N + row] =
-                  __float2bfloat16_rn(g / (1.0f + expf(-g)) * up);
+                  __float2bfloat16_rn(gated_act(act, g, up));
             } else if (EPI == 2) {
               const float up = fmaxf(__uint_as_float(r[j]), 0.f);
               static_cast<__nv_bfloat16*>(out_)[static_cast<size_t>(br) * N + row] = __float2bfloat16_rn(up * up);
@@ -421,7 +421,8 @@ inline bool grouped_usable(int K, int N) {
 // a: [n_blocks * 64, K] bf16 in sorted order; w: [experts * (EPI ? 2 : 1) * N, K]
 template <int EPI>
 inline int launch_grouped(const void* a, const void* w, void* out, const int32_t* sorted_pair, const int32_t* block_expert,
-                          int n_blocks, int experts, int K, int N, cudaStream_t stream) {
+                          int n_blocks, int experts, int K, int N, cudaStream_t stream,
+                          GatedAct act = GatedAct{KLLM_SEQ_ACT_SWIGLU, 0.f, 0.f}) {
   CUtensorMap map_w, map_a;
   if (int rc = make_map(&map_w, w, experts * (EPI == 1 ? 2 : 1) * N, K, BM)) return rc;
   if (int rc = make_map(&map_a, a, n_blocks * GBN, K, GBN)) return rc;
@@ -434,7 +435,7 @@ inline int launch_grouped(const void* a, const void* w, void* out, const int32_t
     configured = true;
   }
   const dim3 grid((N + BM - 1) / BM, n_blocks);
-  umma_grouped_kernel<EPI><<<grid, THREADS, smem, stream>>>(map_w, map_a, out, sorted_pair, block_expert, N, K);
+  umma_grouped_kernel<EPI><<<grid, THREADS, smem, stream>>>(map_w, map_a, out, sorted_pair, block_expert, N, K, act);
   count_launch();
   return static_cast<int>(cudaGetLastError());
 }

@@ -153,20 +153,20 @@ __device__ __forceinline__ void row_stats(const float* buf, int W, int kind, flo
 
 template <typename AT>
 __global__ void embed_kernel(const AT* __restrict__ table, const int32_t* __restrict__ tokens, float* __restrict__ x,
-                             float* __restrict__ copy, NormW norm, float eps, int width) {
+                             float* __restrict__ copy, NormW norm, float eps, float scale, int width) {
   extern __shared__ float buf[];
   __shared__ float red[33];
   const int t = blockIdx.x;
   const AT* row = table + static_cast<size_t>(tokens[t]) * width;
   if (norm.w == nullptr) {
     for (int i = threadIdx.x; i < width; i += blockDim.x) {
-      const float v = to_f(row[i]);
+      const float v = to_f(row[i]) * scale;
       x[static_cast<size_t>(t) * width + i] = v;
       if (copy) copy[static_cast<size_t>(t) * width + i] = v;
     }
     return;
   }
-  for (int i = threadIdx.x; i < width; i += blockDim.x) buf[i] = to_f(row[i]);
+  for (int i = threadIdx.x; i < width; i += blockDim.x) buf[i] = to_f(row[i]) * scale;
   __syncthreads();
   float mean, rstd;
   row_stats(buf, width, norm.kind, eps, red, mean, rstd);
@@ -187,7 +187,7 @@ __device__ void route_token(const RouterArgs& r, const float* xs, float* z, int 
     const float* w = e < experts ? r.w_router + static_cast<size_t>(e) * width : r.w_sg;
     const float acc = warp_dot<float>(w, xs, width, lane);
     if (lane == 0) {
-      if (e < experts) z[e] = acc;
+      if (e < experts) z[e] = acc + (r.bias ? r.bias[e] : 0.f);
       else r.sgate[t] = 1.0f / (1.0f + expf(-acc));
     }
   }
@@ -259,6 +259,37 @@ __device__ void route_token(const RouterArgs& r, const float* xs, float* z, int 
     }
     return;
   }
+  if (r.kind == KLLM_SEQ_ROUTER_TOP_SOFTMAX) {
+    // the largest logits (lowest index on ties); the first chosen is the maximum, so its exponential is 1
+    float first = 0.f, sum = 0.f;
+    for (int k = 0; k < top; ++k) {
+      float best = -INFINITY;
+      int bi = 0x7fffffff;
+      for (int e = lane; e < experts; e += 32) {
+        const float v = z[e];
+        if (v > best) best = v, bi = e;  // ascending e: the lowest index wins a tie inside the lane
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ob = __shfl_xor_sync(kAll, best, o);
+        const int oi = __shfl_xor_sync(kAll, bi, o);
+        if (ob > best || (ob == best && oi < bi)) best = ob, bi = oi;
+      }
+      if (bi == 0x7fffffff) bi = 0;  // logits that are not numbers: kept in range
+      if (k == 0) first = best;
+      const float p = expf(best - first);
+      sum += p;
+      if (lane == 0) {
+        r.top_idx[static_cast<size_t>(t) * top + k] = bi;
+        r.top_w[static_cast<size_t>(t) * top + k] = p;
+        z[bi] = -INFINITY;
+      }
+      __syncwarp();
+    }
+    const float inv = r.scale / sum;
+    for (int k = lane; k < top; k += 32) r.top_w[static_cast<size_t>(t) * top + k] *= inv;
+    return;
+  }
   float mx = -INFINITY;
   for (int e = lane; e < experts; e += 32) mx = fmaxf(mx, z[e]);
   mx = warp_max(mx);
@@ -323,9 +354,13 @@ __global__ void resid_norm_kernel(ResidNormArgs a) {
   const bool changes = a.y1 != nullptr || a.add != nullptr || a.add_rows != nullptr;
   if (a.y1 != nullptr) {
     const float g = a.s2 ? a.s2[r] : 1.0f;
+    const float c1 = a.y1_scale != 0.f ? a.y1_scale : 1.0f, c3 = a.y3_scale != 0.f ? a.y3_scale : 1.0f,
+                c4 = a.y4_scale != 0.f ? a.y4_scale : 1.0f;
     for (int i = threadIdx.x; i < W; i += blockDim.x) {
-      float u = a.y1[src + i];
+      float u = c1 * a.y1[src + i];
+      if (a.y3) u += c3 * a.y3[src + i];
       if (a.y2) u += g * a.y2[src + i];
+      if (a.y4) u += c4 * a.y4[src + i];
       buf[i] = u;
     }
     float mean = 0.f, rstd = 1.f;
@@ -485,8 +520,12 @@ attention_kernel(AttnShape a, const void* __restrict__ q_, PagedKV kv, const int
   const int n_tiles = pmax / kAttnKeys + 1;
   // with a window the first row of the tile sees nothing before its position - window + 1
   const int tile_first = a.window > 0 ? max(0, pos0 + r0 / rep - a.window + 1) / kAttnKeys : 0;
-  const int per = (n_tiles - tile_first + splits - 1) / splits;
-  const int tile_lo = tile_first + split * per, tile_hi = min(n_tiles, tile_lo + per);
+  // tiles before the window that hold kept first positions come ahead of the window's tiles: the list of this CTA's
+  // tiles is [0, keep_tiles) then [tile_first, n_tiles), cut into `splits` parts
+  const int keep_tiles = a.window > 0 ? min(tile_first, (a.keep_first + kAttnKeys - 1) / kAttnKeys) : 0;
+  const int list_n = keep_tiles + n_tiles - tile_first;
+  const int per = (list_n + splits - 1) / splits;
+  const int tile_lo = split * per, tile_hi = min(list_n, tile_lo + per);
 
   const int dq = (a.dim + 3) & ~3, dk = dq + 1;
   extern __shared__ float sm[];
@@ -536,7 +575,8 @@ attention_kernel(AttnShape a, const void* __restrict__ q_, PagedKV kv, const int
   const int rpt = SPARSE ? (rows_here + 1) / 2 : RPT;
   const int my_rows = max(0, min(rpt, rows_here - rg * rpt));
 
-  for (int tile = tile_lo; tile < tile_hi; ++tile) {
+  for (int li = tile_lo; li < tile_hi; ++li) {
+    const int tile = li < keep_tiles ? li : tile_first + (li - keep_tiles);
     const int k0 = tile * kAttnKeys;
     __syncthreads();  // previous tile's K, V, S are no longer read
     if (vec_tiles) {  // 16-byte loads: a key's row is dim / V chunks
@@ -618,8 +658,10 @@ attention_kernel(AttnShape a, const void* __restrict__ q_, PagedKV kv, const int
         if (SPARSE && i >= my_rows) break;  // the softmax below reads only rows that exist
         const int r = rg * rpt + i;
         const int pr = pos0 + (r0 + r) / rep;
-        const bool visible = r < rows_here && kj <= pr && (a.window == 0 || pr - kj < a.window);
-        Ss[r * kAttnKeys + key] = visible ? sc[i] : -INFINITY;
+        const bool visible = r < rows_here && kj <= pr && (a.window == 0 || pr - kj < a.window || kj < a.keep_first);
+        float sv = sc[i];
+        if (a.softcap > 0.f) sv = a.softcap * tanhf(sv / a.softcap);
+        Ss[r * kAttnKeys + key] = visible ? sv : -INFINITY;
       }
     }
     __syncthreads();
@@ -729,7 +771,8 @@ __host__ __device__ inline int pair_rows(int pairs) { return pairs <= 32 ? 4 : 1
 template <typename AT>
 __global__ void expert_gate_up_kernel(const AT* __restrict__ h, const AT* __restrict__ gate_up,
                                       const int32_t* __restrict__ top_idx, AT* __restrict__ inter, int T, int top, int ff,
-                                      int width, SharedExpert sh, int act) {
+                                      int width, SharedExpert sh, GatedAct ga) {
+  const int act = ga.kind;
   extern __shared__ float xs[];  // [width]
   const int pair = blockIdx.x;
   const bool is_shared = pair >= T * top;
@@ -741,7 +784,7 @@ __global__ void expert_gate_up_kernel(const AT* __restrict__ h, const AT* __rest
   for (int i = threadIdx.x; i < width; i += blockDim.x) xs[i] = to_f(h[static_cast<size_t>(t) * width + i]);
   __syncthreads();
   const AT* wg = is_shared ? static_cast<const AT*>(sh.gate_up)
-                           : gate_up + static_cast<size_t>(top_idx[pair]) * (act == KLLM_SEQ_ACT_SWIGLU ? 2 : 1) * ff * width;
+                           : gate_up + static_cast<size_t>(top_idx[pair]) * (act == KLLM_SEQ_ACT_RELU2 ? 1 : 2) * ff * width;
   const AT* wu = wg + static_cast<size_t>(rows) * width;
   AT* dst = is_shared ? static_cast<AT*>(sh.inter) + static_cast<size_t>(t) * sh.ff
                       : inter + static_cast<size_t>(pair) * ff;
@@ -753,10 +796,11 @@ __global__ void expert_gate_up_kernel(const AT* __restrict__ h, const AT* __rest
     }
     return;
   }
+  if (is_shared) ga.limit = sh.limit;
   for (int f = blockIdx.y * kPairRows + warp; f < f_end; f += nw) {
     float gv, uv;
     warp_dot2(wg + static_cast<size_t>(f) * width, wu + static_cast<size_t>(f) * width, xs, width, lane, gv, uv);
-    if (lane == 0) dst[f] = from_f<AT>(gv / (1.0f + expf(-gv)) * uv);
+    if (lane == 0) dst[f] = from_f<AT>(gated_act(ga, gv, uv));
   }
 }
 
@@ -799,13 +843,13 @@ __global__ void combine_pairs_kernel(const float* __restrict__ yp, const float* 
 }
 
 template <typename AT>
-__global__ void silu_mul_kernel(const float* __restrict__ gu, AT* __restrict__ out, int ff, size_t total) {
+__global__ void gated_act_kernel(GatedAct act, const float* __restrict__ gu, AT* __restrict__ out, int ff, size_t total) {
   const size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (i >= total) return;
   const size_t t = i / ff;
   const int f = static_cast<int>(i % ff);
   const float g = gu[t * 2 * ff + f], u = gu[t * 2 * ff + ff + f];
-  out[i] = from_f<AT>(g / (1.0f + expf(-g)) * u);
+  out[i] = from_f<AT>(gated_act(act, g, u));
 }
 
 // ---- greedy id of each logits row (lowest index on ties) ------------------------------------------------------------
@@ -904,11 +948,12 @@ inline int done() {
 }  // namespace
 
 int launch_embed(int dtype, const void* table, const int32_t* tokens, float* x, float* copy, const NormW& norm, float eps,
-                 int T, int width, cudaStream_t s) {
+                 float scale, int T, int width, cudaStream_t s) {
+  if (scale == 0.f) scale = 1.0f;
   const size_t smem = static_cast<size_t>(width) * sizeof(float);
   if (smem > 48 * 1024) return KLLM_E_UNSUPPORTED;
   KLLM_SEQ_DISPATCH(dtype, (embed_kernel<AT><<<T, 128, smem, s>>>(static_cast<const AT*>(table), tokens, x, copy, norm, eps,
-                                                                 width)));
+                                                                 scale, width)));
   return done();
 }
 
@@ -1031,8 +1076,9 @@ bool shared_expert_rides_along(int top, int ff, int shared_ff) {
 }
 
 int launch_expert_gate_up(int dtype, const void* h, const void* gate_up, const int32_t* top_idx, void* inter, int T,
-                          int top, int ff, int width, const SharedExpert& sh, int act, cudaStream_t s) {
-  if (act != KLLM_SEQ_ACT_SWIGLU && (act != KLLM_SEQ_ACT_RELU2 || sh.ff > 0)) return KLLM_E_UNSUPPORTED;
+                          int top, int ff, int width, const SharedExpert& sh, const GatedAct& act, cudaStream_t s) {
+  if (act.kind != KLLM_SEQ_ACT_SWIGLU && act.kind != KLLM_SEQ_ACT_CLAMP_SWIGLU && (act.kind != KLLM_SEQ_ACT_RELU2 || sh.ff > 0))
+    return KLLM_E_UNSUPPORTED;
   const size_t smem = static_cast<size_t>(width) * sizeof(float);
   if (smem > 48 * 1024) return KLLM_E_UNSUPPORTED;
   const int kPairRows = pair_rows(T * top);
@@ -1061,10 +1107,10 @@ int launch_combine_pairs(const float* yp, const float* top_w, float* y, int T, i
   return done();
 }
 
-int launch_silu_mul(int dtype, const float* gu, void* out, int T, int ff, cudaStream_t s) {
+int launch_gated_act(int dtype, const GatedAct& act, const float* gu, void* out, int T, int ff, cudaStream_t s) {
   const size_t total = static_cast<size_t>(T) * ff;
   const unsigned blocks = static_cast<unsigned>((total + 255) / 256);
-  KLLM_SEQ_DISPATCH(dtype, (silu_mul_kernel<AT><<<blocks, 256, 0, s>>>(gu, static_cast<AT*>(out), ff, total)));
+  KLLM_SEQ_DISPATCH(dtype, (gated_act_kernel<AT><<<blocks, 256, 0, s>>>(act, gu, static_cast<AT*>(out), ff, total)));
   return done();
 }
 

@@ -553,9 +553,12 @@ __global__ void activation_kernel(int act, float a, float b, const float* __rest
   out[i] = from_f<AT>(r);
 }
 
-__global__ void scale_kernel(float* __restrict__ v, float scale, size_t n) {
+__global__ void scale_kernel(float* __restrict__ v, float scale, float cap, size_t n) {
   const size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-  if (i < n) v[i] *= scale;
+  if (i >= n) return;
+  float z = v[i] * scale;
+  if (cap > 0.f) z = cap * tanhf(z / cap);
+  v[i] = z;
 }
 
 #define KLLM_SEQ_DISPATCH(dtype, CALL)                         \
@@ -689,8 +692,8 @@ int launch_activation(int dtype, int act, float a, float b, const float* z, void
   return done();
 }
 
-int launch_scale(float* v, float scale, size_t n, cudaStream_t s) {
-  scale_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, s>>>(v, scale, n);
+int launch_scale(float* v, float scale, float cap, size_t n, cudaStream_t s) {
+  scale_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, s>>>(v, scale == 0.f ? 1.0f : scale, cap, n);
   return done();
 }
 

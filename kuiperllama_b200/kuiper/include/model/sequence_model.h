@@ -85,6 +85,9 @@ class SequenceModel : public base::NoCopyable {
   base::Status upload_broadcast(const StTensor* t, int64_t numel, const float** device);
   // the values of a small tensor on the host, checked against `numel`
   base::Status read_values(const StTensor* t, int64_t numel, std::vector<float>* out) const;
+  // several tensors one after the other as fp32 on the device; each must hold numel[i] values
+  base::Status upload_f32_parts(const std::vector<const StTensor*>& parts, const std::vector<int64_t>& numel,
+                                const float** device);
 
   ComputeType compute_ = ComputeType::kBFloat16;
   int32_t vocab_ = 0, width_ = 0;
@@ -98,6 +101,8 @@ class SequenceModel : public base::NoCopyable {
   kllm_seq_norm embed_norm_{nullptr, nullptr, KLLM_SEQ_NORM_LAYER};  // w == nullptr: the embedding rows are used as they are
   std::vector<int32_t> run_embed_;  // per layer run (or empty): add the embedding output before the run
   float logit_scale_ = 1.0f;
+  float embed_scale_ = 1.0f;    // the embedding rows are multiplied by it
+  float logit_softcap_ = 0.0f;  // logits <- cap * tanh(logits / cap); 0: none
 
  private:
   SequenceOptions options_;

@@ -92,6 +92,16 @@ base::Status SequenceModel::read_values(const StTensor* t, int64_t numel, std::v
   return tensor_to_f32(*t, out->data());
 }
 
+base::Status SequenceModel::upload_f32_parts(const std::vector<const StTensor*>& parts, const std::vector<int64_t>& numel,
+                                             const float** device) {
+  std::vector<float> all, one;
+  for (size_t i = 0; i < parts.size(); ++i) {
+    if (base::Status st = read_values(parts[i], numel[i], &one); !st) return st;
+    all.insert(all.end(), one.begin(), one.end());
+  }
+  return upload_values(all, device);
+}
+
 base::Status SequenceModel::upload_broadcast(const StTensor* t, int64_t numel, const float** device) {
   std::vector<float> one;
   if (base::Status st = read_values(t, 1, &one); !st) return st;
@@ -133,6 +143,7 @@ base::Status SequenceModel::init(const std::string& dir, const SequenceOptions& 
   d.run_vectors = run_vectors_, d.embed = embed_, d.final_norm = final_norm_, d.head = head_;
   d.max_tokens = options.max_tokens, d.max_seqs = options.max_seqs, d.page_tokens = options.page_tokens;
   d.embed_norm = embed_norm_, d.logit_scale = logit_scale_;
+  d.embed_scale = embed_scale_, d.logit_softcap = logit_softcap_;
   d.run_embed = run_embed_.size() == run_layer_.size() ? run_embed_.data() : nullptr;
   return engine_status(kllm_seq_create(&d, nullptr, &engine_), "kllm_seq_create");
 }
