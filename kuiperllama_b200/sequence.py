@@ -2,7 +2,7 @@
 device memory, the engine and every kernel are the product library's.  Like the rest of this package it has no
 fallback: without libkllm_seq.so (or libkllm_b200.so, which carries the same symbols) it raises.
 
-`FobolornShape` / `KikunexShape` + `SeqEngine` build a random-weight model of a family directly in device memory
+`FobolornShape` / `KikunexShape` / `VurazenShape` + `SeqEngine` build a random-weight model of a family directly in device memory
 (no model folder), for measurements at sizes that resemble a real model's layers.
 """
 from __future__ import annotations
@@ -23,7 +23,10 @@ class Norm(ctypes.Structure):
 class Attention(ctypes.Structure):
     _fields_ = [("heads", c_int32), ("kv_heads", c_int32), ("dim", c_int32), ("vdim", c_int32), ("scale", c_float),
                 ("temp_coef", c_float), ("temp_every", c_int32), ("qk_norm", c_int32), ("gate", c_int32),
-                ("w_in", c_void_p), ("q_norm_w", c_void_p), ("k_norm_w", c_void_p), ("w_out", c_void_p)]
+                ("w_in", c_void_p), ("q_norm_w", c_void_p), ("k_norm_w", c_void_p), ("w_out", c_void_p),
+                ("window", c_int32), ("keep_first", c_int32), ("softcap", c_float), ("sink", c_void_p),
+                ("in_bias", c_void_p), ("conv_taps", c_int32), ("conv_w", c_void_p), ("rope_dims", c_int32),
+                ("rope_base", c_float), ("rope_pairing", c_int32), ("values_are_keys", c_int32)]
 
 
 class Moe(ctypes.Structure):
@@ -31,7 +34,8 @@ class Moe(ctypes.Structure):
                 ("w_router", c_void_p), ("gate_up", c_void_p), ("down", c_void_p), ("shared_ff", c_int32),
                 ("shared_gate_up", c_void_p), ("shared_down", c_void_p), ("w_shared_gate", c_void_p),
                 ("router_kind", c_int32), ("correction", c_void_p), ("groups", c_int32), ("groups_keep", c_int32),
-                ("act", c_int32)]
+                ("act", c_int32), ("router_bias", c_void_p), ("act_limit", c_float), ("act_alpha", c_float),
+                ("shared_act_limit", c_float)]
 
 
 class Latent(ctypes.Structure):
@@ -51,10 +55,24 @@ class Dense(ctypes.Structure):
                 ("down", c_void_p)]
 
 
+class Ssm(ctypes.Structure):
+    _fields_ = [("inner", c_int32), ("state", c_int32), ("dt_rank", c_int32), ("conv_taps", c_int32), ("w_in", c_void_p),
+                ("conv_w", c_void_p), ("conv_b", c_void_p), ("w_x", c_void_p), ("w_dt", c_void_p), ("dt_b", c_void_p),
+                ("a", c_void_p), ("d", c_void_p), ("w_out", c_void_p)]
+
+
+class Delta(ctypes.Structure):
+    _fields_ = [("heads", c_int32), ("kv_heads", c_int32), ("dim", c_int32), ("vdim", c_int32), ("conv_taps", c_int32),
+                ("decay_rank", c_int32), ("gate_rank", c_int32), ("w_in", c_void_p), ("conv_w", c_void_p),
+                ("w_a2", c_void_p), ("dt_bias", c_void_p), ("rate", c_void_p), ("w_g2", c_void_p),
+                ("out_norm_w", c_void_p), ("w_out", c_void_p)]
+
+
 class Layer(ctypes.Structure):
     _fields_ = [("mixer_kind", c_int32), ("ff_kind", c_int32), ("pre_mixer", Norm), ("post_mixer", Norm),
                 ("pre_ff", Norm), ("post_ff", Norm), ("attn", Attention), ("moe", Moe), ("shift", c_void_p),
-                ("latent", Latent), ("linear", Linear), ("dense", Dense)]
+                ("latent", Latent), ("linear", Linear), ("dense", Dense), ("ssm", Ssm), ("delta", Delta),
+                ("mixer2_kind", c_int32), ("mixer_scale", c_float), ("mixer2_scale", c_float), ("parallel_ff", c_int32)]
 
 
 class Desc(ctypes.Structure):
@@ -62,7 +80,8 @@ class Desc(ctypes.Structure):
                 ("n_layers", c_int32), ("layers", POINTER(Layer)), ("n_runs", c_int32), ("run_layer", POINTER(c_int32)),
                 ("run_add", POINTER(c_int32)), ("run_vectors", c_void_p), ("embed", c_void_p), ("final_norm", Norm),
                 ("head", c_void_p), ("max_tokens", c_int32), ("max_seqs", c_int32), ("page_tokens", c_int32),
-                ("embed_norm", Norm), ("run_embed", POINTER(c_int32)), ("logit_scale", c_float)]
+                ("embed_norm", Norm), ("run_embed", POINTER(c_int32)), ("logit_scale", c_float), ("embed_scale", c_float),
+                ("logit_softcap", c_float)]
 
 
 class SeqError(RuntimeError):
@@ -223,8 +242,107 @@ class KikunexShape:
         return total
 
 
+@dataclass
+class VurazenShape:
+    """A Vurazen model: `pattern` lists the layers ("mamba" | "lightning" | "parallel", "dense" | "moe" | None)."""
+    name: str
+    width: int
+    vocab: int
+    pattern: tuple
+    loop: tuple          # (start, stop, times)
+    inner: int           # selective scan
+    state: int
+    dt_rank: int
+    lin_heads: int       # linear attention
+    lin_dim: int
+    lin_vdim: int
+    heads: int           # window attention (values = keys)
+    kv_heads: int
+    dim: int
+    window: int
+    keep_first: int
+    rot_dims: int
+    d_heads: int         # delta rule
+    d_kv_heads: int
+    d_dim: int
+    d_vdim: int
+    d_rank: int
+    dense_ff: int
+    experts: int
+    top: int
+    ff: int
+    shared_ff: int
+    taps: int = 4
+    eps: float = 1e-5
+
+    @property
+    def layers(self):
+        return len(self.pattern)
+
+    def run_order(self):
+        s, e, t = self.loop
+        order = [(i, -1, 0) for i in range(s)]
+        for p in range(t):
+            order += [(i, p if i == s else -1, 1 if i == s and p > 0 else 0) for i in range(s, e)]
+        return order + [(i, -1, 0) for i in range(e, self.layers)]
+
+    @property
+    def runs(self):
+        return len(self.run_order())
+
+    def delta_in(self):
+        return 2 * self.d_kv_heads * self.d_dim + self.d_heads * self.d_vdim + self.d_heads + 2 * self.d_rank
+
+    def mixer_weight_elems(self, kind):
+        W = self.width
+        if kind == "mamba":
+            return 2 * self.inner * W + (self.dt_rank + 2 * self.state) * self.inner + self.inner * self.dt_rank + W * self.inner
+        if kind == "lightning":
+            return 2 * self.lin_heads * (self.lin_dim + self.lin_vdim) * W + W * self.lin_heads * self.lin_vdim
+        left = (self.heads + self.kv_heads) * self.dim * W + W * self.heads * self.dim
+        right = self.delta_in() * W + self.d_heads * (self.d_dim + self.d_vdim) * self.d_rank + W * self.d_heads * self.d_vdim
+        return left + right
+
+    def ff_weight_elems(self, kind, pairs):
+        W = self.width
+        if kind == "dense":
+            return 3 * self.dense_ff * W
+        if kind == "moe":
+            return self.experts * W + min(pairs, self.experts) * 3 * self.ff * W + 3 * self.shared_ff * W
+        return 0
+
+    def weight_elems_per_step(self, batch):
+        """Matrix elements a decode step of `batch` sequences reads (distinct experts: an upper bound)."""
+        total = self.vocab * self.width
+        for i, _, _ in self.run_order():
+            m, f = self.pattern[i]
+            total += self.mixer_weight_elems(m) + self.ff_weight_elems(f, batch * self.top)
+        return total
+
+    def flops_per_token(self):
+        total = self.vocab * self.width
+        for i, _, _ in self.run_order():
+            m, f = self.pattern[i]
+            total += self.mixer_weight_elems(m) + self.ff_weight_elems(f, self.top)
+        return 2 * total
+
+    def state_bytes_per_step(self, batch, ctx, es):
+        """Cache and state a decode step touches: the window's keys and values, the recurrent states (read and written)."""
+        total = 0
+        for i, _, _ in self.run_order():
+            m, _ = self.pattern[i]
+            if m == "mamba":
+                total += batch * 2 * self.inner * self.state * 4
+            elif m == "lightning":
+                total += batch * 2 * self.lin_heads * self.lin_dim * self.lin_vdim * 4
+            else:
+                total += batch * min(ctx, self.window + self.keep_first) * 2 * self.kv_heads * self.dim * es
+                total += batch * 2 * self.d_heads * self.d_dim * self.d_vdim * 4
+        return total
+
+
 class SeqEngine:
-    """A random-weight model (Fobolorn or Kikunex, by the shape's class) in device memory behind the engine's C-ABI."""
+    """A random-weight model (Fobolorn, Kikunex or Vurazen, by the shape's class) in device memory behind the engine's C-ABI."""
 
     def __init__(self, shape, dtype=BF16, max_tokens=4096, max_seqs=16, page=0, seed=1):
         import torch
@@ -233,6 +351,9 @@ class SeqEngine:
         self.shape, self.dtype = shape, dtype
         if isinstance(shape, KikunexShape):
             self._init_kikunex(shape, dtype, max_tokens, max_seqs, page, seed)
+            return
+        if isinstance(shape, VurazenShape):
+            self._init_vurazen(shape, dtype, max_tokens, max_seqs, page, seed)
             return
         td = torch.bfloat16 if dtype == BF16 else torch.float32
         g = torch.Generator(device="cuda").manual_seed(seed)
@@ -367,6 +488,119 @@ class SeqEngine:
         d.embed_norm, d.final_norm = norm(), norm()
         d.head = rnd(shape.vocab, W, std=W ** -0.5).data_ptr()
         d.logit_scale = 0.5
+        d.max_tokens, d.max_seqs, d.page_tokens = max_tokens, max_seqs, page
+        self._desc = (d, layers, run_layer, run_add, run_embed)
+        self.handle = c_void_p()
+        torch.cuda.synchronize()
+        _check(self.lib, self.lib.kllm_seq_create(ctypes.byref(d), None, ctypes.byref(self.handle)), "kllm_seq_create")
+
+    def _init_vurazen(self, shape, dtype, max_tokens, max_seqs, page, seed):
+        torch = self.torch
+        td = torch.bfloat16 if dtype == BF16 else torch.float32
+        g = torch.Generator(device="cuda").manual_seed(seed)
+        keep = self._keep = []
+        W = shape.width
+
+        def rnd(*dims, std, t=td, mean=0.0):
+            x = (torch.randn(*dims, device="cuda", generator=g) * std + mean).to(t).contiguous()
+            keep.append(x)
+            return x
+
+        def f32(*dims, std, mean=0.0):
+            return rnd(*dims, std=std, t=torch.float32, mean=mean)
+
+        def norm():
+            return Norm(f32(W, std=0.05, mean=1.0).data_ptr(), f32(W, std=0.05).data_ptr(), 0)
+
+        layers = (Layer * shape.layers)()
+        for L, (mix, ff) in zip(layers, shape.pattern):
+            L.pre_mixer = norm()
+            L.mixer_scale = L.mixer2_scale = 1.0
+            if mix == "mamba":
+                L.mixer_kind = 4
+                a = L.ssm
+                n = shape.inner
+                a.inner, a.state, a.dt_rank, a.conv_taps = n, shape.state, shape.dt_rank, shape.taps
+                a.w_in = rnd(2 * n, W, std=W ** -0.5).data_ptr()
+                a.conv_w = f32(n, shape.taps, std=0.5).data_ptr()
+                a.conv_b = f32(n, std=0.1).data_ptr()
+                a.w_x = rnd(shape.dt_rank + 2 * shape.state, n, std=n ** -0.5).data_ptr()
+                a.w_dt = f32(n, shape.dt_rank, std=shape.dt_rank ** -0.5).data_ptr()
+                a.dt_b = f32(n, std=0.5, mean=-2.0).data_ptr()
+                rates = -torch.rand(n, shape.state, device="cuda", generator=g) * 4.0 - 0.05
+                keep.append(rates)
+                a.a = rates.data_ptr()
+                a.d = f32(n, std=1.0).data_ptr()
+                a.w_out = rnd(W, n, std=0.5 * n ** -0.5).data_ptr()
+            elif mix == "lightning":
+                L.mixer_kind = 3
+                a = L.linear
+                a.heads, a.dim, a.vdim = shape.lin_heads, shape.lin_dim, shape.lin_vdim
+                decay = torch.tensor([math.exp(-1.0 / (4.0 * (h + 1))) for h in range(shape.lin_heads)], device="cuda")
+                keep.append(decay)
+                a.decay = decay.data_ptr()
+                a.w_in = rnd(2 * shape.lin_heads * (shape.lin_dim + shape.lin_vdim), W, std=W ** -0.5).data_ptr()
+                a.out_norm_w = f32(shape.lin_heads * shape.lin_vdim, std=0.05, mean=1.0).data_ptr()
+                a.w_out = rnd(W, shape.lin_heads * shape.lin_vdim, std=(shape.lin_heads * shape.lin_vdim) ** -0.5).data_ptr()
+            else:
+                L.mixer_kind, L.mixer2_kind = 1, 5
+                L.mixer_scale, L.mixer2_scale = 0.6, 0.5
+                a = L.attn
+                a.heads, a.kv_heads, a.dim, a.vdim = shape.heads, shape.kv_heads, shape.dim, shape.dim
+                C = (shape.heads + shape.kv_heads) * shape.dim
+                a.scale, a.softcap, a.window, a.keep_first = shape.dim ** -0.5, 30.0, shape.window, shape.keep_first
+                a.conv_taps, a.rope_dims, a.rope_base, a.rope_pairing, a.values_are_keys = shape.taps, shape.rot_dims, 1e4, 1, 1
+                a.w_in = rnd(C, W, std=W ** -0.5).data_ptr()
+                a.in_bias = f32(C, std=0.1).data_ptr()
+                a.conv_w = f32(C, shape.taps, std=0.5).data_ptr()
+                a.sink = f32(shape.heads, std=1.0).data_ptr()
+                a.w_out = rnd(W, shape.heads * shape.dim, std=(shape.heads * shape.dim) ** -0.5).data_ptr()
+                b = L.delta
+                b.heads, b.kv_heads, b.dim, b.vdim = shape.d_heads, shape.d_kv_heads, shape.d_dim, shape.d_vdim
+                b.conv_taps, b.decay_rank, b.gate_rank = shape.taps, shape.d_rank, shape.d_rank
+                Cd = 2 * shape.d_kv_heads * shape.d_dim + shape.d_heads * shape.d_vdim
+                b.w_in = rnd(shape.delta_in(), W, std=W ** -0.5).data_ptr()
+                b.conv_w = f32(Cd, shape.taps, std=0.5).data_ptr()
+                b.w_a2 = f32(shape.d_heads * shape.d_dim, shape.d_rank, std=shape.d_rank ** -0.5).data_ptr()
+                b.dt_bias = f32(shape.d_heads * shape.d_dim, std=0.5, mean=-2.0).data_ptr()
+                rate = torch.rand(shape.d_heads, device="cuda", generator=g) * 2.0 + 0.02
+                keep.append(rate)
+                b.rate = rate.data_ptr()
+                b.w_g2 = f32(shape.d_heads * shape.d_vdim, shape.d_rank, std=shape.d_rank ** -0.5).data_ptr()
+                b.out_norm_w = f32(shape.d_vdim, std=0.05, mean=1.0).data_ptr()
+                b.w_out = rnd(W, shape.d_heads * shape.d_vdim, std=(shape.d_heads * shape.d_vdim) ** -0.5).data_ptr()
+            L.ff_kind = {None: 0, "moe": 1, "dense": 2}[ff]
+            L.parallel_ff = 0 if ff is None else 1
+            if ff == "dense":
+                d = L.dense
+                d.ff, d.act = shape.dense_ff, 3
+                d.up = rnd(2 * shape.dense_ff, W, std=W ** -0.5).data_ptr()
+                d.down = rnd(W, shape.dense_ff, std=0.3 * shape.dense_ff ** -0.5).data_ptr()
+            elif ff == "moe":
+                m = L.moe
+                m.experts, m.top, m.ff, m.router_scale = shape.experts, shape.top, shape.ff, 1.0
+                m.router_kind, m.act, m.act_limit, m.act_alpha, m.shared_act_limit = 2, 4, 7.0, 1.702, 7.0
+                m.w_router = f32(shape.experts, W, std=W ** -0.5).data_ptr()
+                m.router_bias = f32(shape.experts, std=0.1).data_ptr()
+                m.gate_up = rnd(shape.experts, 2 * shape.ff, W, std=W ** -0.5).data_ptr()
+                m.down = rnd(shape.experts, W, shape.ff, std=0.3 * shape.ff ** -0.5).data_ptr()
+                m.shared_ff = shape.shared_ff
+                if shape.shared_ff:
+                    m.shared_gate_up = rnd(2 * shape.shared_ff, W, std=W ** -0.5).data_ptr()
+                    m.shared_down = rnd(W, shape.shared_ff, std=0.3 * shape.shared_ff ** -0.5).data_ptr()
+        order = shape.run_order()
+        run_layer = (c_int32 * len(order))(*[i for i, _, _ in order])
+        run_add = (c_int32 * len(order))(*[p for _, p, _ in order])
+        run_embed = (c_int32 * len(order))(*[x for _, _, x in order])
+        d = Desc()
+        d.dtype, d.width, d.vocab, d.norm_eps = dtype, W, shape.vocab, shape.eps
+        d.n_layers, d.layers = shape.layers, layers
+        d.n_runs, d.run_layer, d.run_add, d.run_embed = len(order), run_layer, run_add, run_embed
+        d.run_vectors = f32(max(1, shape.loop[2]), W, std=0.1).data_ptr()
+        d.embed = rnd(shape.vocab, W, std=1.0).data_ptr()
+        d.final_norm = norm()
+        d.head = rnd(shape.vocab, W, std=W ** -0.5).data_ptr()
+        d.embed_scale, d.logit_softcap = 1.0, 30.0
         d.max_tokens, d.max_seqs, d.page_tokens = max_tokens, max_seqs, page
         self._desc = (d, layers, run_layer, run_add, run_embed)
         self.handle = c_void_p()

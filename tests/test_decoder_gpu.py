@@ -47,7 +47,9 @@ def load_decoder(path, quant=False, flavour="llama2", qkv_bias=None):
 
 @pytest.fixture(scope="module")
 def ref():
-    from oracle.binding import RefCuda
+    from oracle.binding import REF_SO, RefCuda
+    if not REF_SO.exists():
+        pytest.skip("the reference's library is not built here (its source tree is absent)")
     return RefCuda("llama2")
 
 

@@ -16,13 +16,17 @@ pytestmark = pytest.mark.gpu
 
 @pytest.fixture(scope="module")
 def ref():
-    from oracle.binding import RefCuda
+    from oracle.binding import REF_SO, RefCuda
+    if not REF_SO.exists():
+        pytest.skip("the reference's library is not built here (its source tree is absent)")
     return RefCuda("llama2")
 
 
 @pytest.fixture(scope="module")
 def ref_qwen():
-    from oracle.binding import RefCuda
+    from oracle.binding import REF_QWEN_SO, RefCuda
+    if not REF_QWEN_SO.exists():
+        pytest.skip("the reference's library is not built here (its source tree is absent)")
     return RefCuda("qwen2")
 
 
@@ -247,7 +251,9 @@ def test_gemv_fused_matches_op_chain(kllm_lib, ref, oracle):
     for i, (w, b, o, rows) in enumerate([(wq, bq, q, dim), (wk, bk, k, kvd), (wv, bv, v, kvd)]):
         job.seg[i].w = w.data_ptr(); job.seg[i].bias = b.data_ptr(); job.seg[i].out = o.data_ptr(); job.seg[i].rows = rows
     assert kllm_lib.kllm_gemv_fused(ctypes.byref(job), None) == 0
-    from oracle.binding import RefCuda
+    from oracle.binding import REF_QWEN_SO, RefCuda
+    if not REF_QWEN_SO.exists():
+        pytest.skip("the reference's library is not built here (its source tree is absent)")
     rq = RefCuda("qwen2")
     xn = torch.zeros(dim, device="cuda"); rq.L.kref_rmsnorm(ptr(x), ptr(nw), ptr(xn), dim, None)
     for w, b, o, rows, name in [(wq, bq, q, dim, "q"), (wk, bk, k, kvd, "k"), (wv, bv, v, kvd, "v")]:
