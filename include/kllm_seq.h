@@ -75,7 +75,8 @@ typedef struct kllm_seq_attention {
   const float* in_bias;  /* [rows of w_in] fp32 added to the projection, or NULL */
   int32_t conv_taps;     /* > 1: a causal convolution over time on every query and key channel, right after the projection
                             (zeros before the sequence's start; the last conv_taps - 1 projected rows are state of the sequence) */
-  const float* conv_w;   /* [heads*dim + kv_heads*dim][conv_taps] fp32, the last column weighs the current token */
+  const float* conv_w;   /* [heads*dim + kv_heads*dim][conv_taps] fp32, the last column weighs the current token
+                            (NULL: no filter; with conv_taps == 1 it is one weight per channel) */
   int32_t rope_dims;     /* rotary positions on the first rope_dims coordinates of every query and key head; 0: none */
   float rope_base;       /* angle of pair i = position * rope_base^(-2 i / rope_dims) */
   int32_t rope_pairing;  /* KLLM_SEQ_ROPE_* */
@@ -189,7 +190,7 @@ typedef struct kllm_seq_layer {
   kllm_seq_ssm ssm;
   kllm_seq_delta delta;
   /* A second mixer of another kind beside the first (0: none): both read the same input and the mixer's output is
-   * mixer_scale * first + mixer2_scale * second. */
+   * mixer_scale * first + mixer2_scale * second (the scales are read only when there is a second mixer). */
   int32_t mixer2_kind;
   float mixer_scale, mixer2_scale;
   /* != 0: the feed-forward reads the mixer's input too (pre_mixer's output; pre_ff is not used) and

@@ -183,11 +183,11 @@ static int validate_mixer(const kllm_seq_layer& L, int kind) {
     if (a.qk_norm && (!a.q_norm_w || !a.k_norm_w)) return KLLM_E_INVALID;
     if (a.vdim > 256 || a.dim > 512) return KLLM_E_UNSUPPORTED;
     if (a.window < 0 || a.keep_first < 0 || a.softcap < 0.f || a.conv_taps < 0 || a.rope_dims < 0 || a.rope_dims > a.dim ||
-        (a.rope_dims & 1) || (a.rope_dims > 0 && a.rope_base <= 0.f) || (a.conv_taps > 1 && !a.conv_w))
+        (a.rope_dims & 1) || (a.rope_dims > 0 && a.rope_base <= 0.f))
       return KLLM_E_INVALID;
     if (a.values_are_keys && a.vdim != a.dim) return KLLM_E_INVALID;
     // the filtered, rotated form has its own preparation kernel: no head norms, temperature or gate there
-    const bool prep2 = a.values_are_keys || a.conv_taps > 1 || a.rope_dims > 0 || a.in_bias;
+    const bool prep2 = a.values_are_keys || a.conv_taps > 1 || a.conv_w || a.rope_dims > 0 || a.in_bias;
     if (prep2 && (!a.values_are_keys || a.qk_norm || a.gate || a.temp_every)) return KLLM_E_UNSUPPORTED;
   } else if (kind == KLLM_SEQ_MIXER_LATENT) {
     const kllm_seq_latent& a = L.latent;
@@ -203,14 +203,14 @@ static int validate_mixer(const kllm_seq_layer& L, int kind) {
     if (a.dim > 256) return KLLM_E_UNSUPPORTED;
   } else if (kind == KLLM_SEQ_MIXER_SSM) {
     const kllm_seq_ssm& a = L.ssm;
-    if (a.inner <= 0 || a.state <= 0 || a.dt_rank <= 0 || a.conv_taps < 1 || !a.w_in || (a.conv_taps > 1 && !a.conv_w) ||
+    if (a.inner <= 0 || a.state <= 0 || a.dt_rank <= 0 || a.conv_taps < 1 || !a.w_in ||
         !a.w_x || !a.w_dt || !a.dt_b || !a.a || !a.d || !a.w_out)
       return KLLM_E_INVALID;
     if (a.state > 128) return KLLM_E_UNSUPPORTED;
   } else if (kind == KLLM_SEQ_MIXER_DELTA) {
     const kllm_seq_delta& a = L.delta;
     if (a.heads <= 0 || a.kv_heads <= 0 || a.heads % a.kv_heads || a.dim <= 0 || a.vdim <= 0 || a.conv_taps < 1 ||
-        a.decay_rank <= 0 || a.gate_rank <= 0 || !a.w_in || (a.conv_taps > 1 && !a.conv_w) || !a.w_a2 || !a.dt_bias ||
+        a.decay_rank <= 0 || a.gate_rank <= 0 || !a.w_in || !a.w_a2 || !a.dt_bias ||
         !a.rate || !a.w_g2 || !a.out_norm_w || !a.w_out)
       return KLLM_E_INVALID;
     if (a.dim > 1024) return KLLM_E_UNSUPPORTED;
@@ -621,7 +621,7 @@ extern "C" int kllm_seq_step(kllm_seq_engine* e, int32_t n_entries, const int32_
   // the kernel when every entry is one token, else by a kernel of its own on the fp32 rows.
   auto router_args = [&](const kllm_seq_moe& M) {
     return RouterArgs{M.w_router, M.shared_ff > 0 ? M.w_shared_gate : nullptr, M.experts, M.top,
-                      M.router_scale != 0.f ? M.router_scale : 1.0f, static_cast<int32_t*>(e->top_idx.p),
+                      M.router_scale, static_cast<int32_t*>(e->top_idx.p),
                       static_cast<float*>(e->top_w.p), static_cast<float*>(e->sgate.p), M.router_kind, M.correction,
                       M.groups, M.groups_keep, M.router_bias};
   };
@@ -850,8 +850,8 @@ extern "C" int kllm_seq_step(kllm_seq_engine* e, int32_t n_entries, const int32_
     if (L.mixer2_kind != 0) RC(run_mixer(L, L.mixer2_kind, r, y3));
     // what the mixers add to x: c1 y (+ c3 y3)
     ResidNormArgs mixed{};
-    mixed.y1 = y, mixed.y1_scale = L.mixer_scale;
-    if (L.mixer2_kind != 0) mixed.y3 = y3, mixed.y3_scale = L.mixer2_scale;
+    mixed.y1 = y;
+    if (L.mixer2_kind != 0) mixed.c1 = L.mixer_scale, mixed.y3 = y3, mixed.c3 = L.mixer2_scale;
 
     // what follows this layer run: the next run's additions and pre-norm can ride on this run's last kernel
     const bool fuse_next = r + 1 < d.n_runs && !tracing;

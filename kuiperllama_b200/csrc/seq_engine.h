@@ -126,7 +126,7 @@ struct ResidNormArgs {
   ShiftArgs shift;        // inline token shift (single-token steps)
   const float* y3;        // further addends of the sum that joins x (with y1)
   const float* y4;
-  float y1_scale, y3_scale, y4_scale;  // their coefficients c1, c3, c4; 0 means 1
+  float c1 = 1.0f, c3 = 1.0f, c4 = 1.0f;  // the coefficients of y1, y3, y4
 };
 int launch_resid_norm(const ResidNormArgs& a, cudaStream_t s);
 

@@ -354,8 +354,7 @@ __global__ void resid_norm_kernel(ResidNormArgs a) {
   const bool changes = a.y1 != nullptr || a.add != nullptr || a.add_rows != nullptr;
   if (a.y1 != nullptr) {
     const float g = a.s2 ? a.s2[r] : 1.0f;
-    const float c1 = a.y1_scale != 0.f ? a.y1_scale : 1.0f, c3 = a.y3_scale != 0.f ? a.y3_scale : 1.0f,
-                c4 = a.y4_scale != 0.f ? a.y4_scale : 1.0f;
+    const float c1 = a.c1, c3 = a.c3, c4 = a.c4;
     for (int i = threadIdx.x; i < W; i += blockDim.x) {
       float u = c1 * a.y1[src + i];
       if (a.y3) u += c3 * a.y3[src + i];

@@ -82,7 +82,7 @@ __device__ __forceinline__ float conv_at(const float* __restrict__ in, int strid
     if (sp < 0) continue;
     const float u = sp >= p.pos0 ? in[static_cast<size_t>(p.first + sp - p.pos0) * stride + c] + b
                                  : st[static_cast<size_t>(hist - (p.pos0 - sp)) * C + c];
-    acc = fmaf(w[c * taps + k], u, acc);
+    acc = fmaf(w ? w[c * taps + k] : (k == hist ? 1.0f : 0.f), u, acc);  // no weights: the row itself
   }
   return acc;
 }
@@ -454,7 +454,7 @@ inline int lanes_for(int n, int per) {
 int launch_qk_conv_prepare(int dtype, const AttnShape& a, const AttnPrep& p, const float* qk, const StepRows& rows, void* q,
                            const PagedKV& kv, int T, cudaStream_t s) {
   const int C = (a.heads + a.kv_heads) * a.dim;
-  if (p.taps < 1 || (p.taps > 1 && (!p.conv_w || !p.conv_state)) || (p.rope_dims & 1) || p.rope_dims > a.dim) return KLLM_E_INVALID;
+  if (p.taps < 1 || (p.taps > 1 && !p.conv_state) || (p.rope_dims & 1) || p.rope_dims > a.dim) return KLLM_E_INVALID;
   const size_t smem = static_cast<size_t>(C) * sizeof(float);
   if (smem > 48 * 1024) return KLLM_E_UNSUPPORTED;
   const int threads = C >= 2048 ? 512 : 256;
@@ -474,7 +474,8 @@ int launch_ssm_scan(int dtype, const kllm_seq_ssm& m, const float* uz, const flo
                     const StepRows& rows, const int32_t* ent_seq, int max_count, void* out, cudaStream_t s) {
   (void)max_count;
   if (m.state > 32 * kScanPerLane) return KLLM_E_UNSUPPORTED;
-  const int L = lanes_for(m.state, kScanPerLane > 1 && m.state > 32 ? kScanPerLane : 1);
+  // at least 4 lanes per channel: at most 32 channels of a chunk in shared memory
+  const int L = std::max(4, lanes_for(m.state, m.state > 32 ? kScanPerLane : 1));
   const int CH = kScanThreads / L;
   const size_t smem = (static_cast<size_t>(kScanChunk) * (m.dt_rank + 2 * m.state) + 4 * static_cast<size_t>(kScanChunk) * CH) *
                       sizeof(float);

@@ -89,7 +89,7 @@ base::Status VurazenModel::build_window_attention(const json::Value& c, const Sa
   a->heads = get_int(c, "heads"), a->kv_heads = get_int(c, "kv_heads"), a->dim = get_int(c, "dim"), a->vdim = get_int(c, "vdim");
   a->scale = get_float(c, "scale");
   a->softcap = present(c, "softcap") ? get_float(c, "softcap") : 0.f;
-  a->conv_taps = present(c, "conv") ? get_int(c, "conv") : 1;
+  a->conv_taps = get_int(c, "conv");
   a->window = 0, a->keep_first = 0;
   if (present(c, "mask")) {
     a->window = get_int(c.at("mask"), "size");
@@ -113,8 +113,7 @@ base::Status VurazenModel::build_window_attention(const json::Value& c, const Sa
   if (st = upload_compute({o}, int64_t(a->heads) * a->vdim, &a->w_out); !st) return st;
   if (st = upload_f32_parts({qb, kb}, {qn, kn}, &a->in_bias); !st) return st;
   if (st = upload_f32(sink, a->heads, &a->sink); !st) return st;
-  a->conv_w = nullptr;
-  if (a->conv_taps > 1) {
+  {  // a filter of one tap is still a weight per channel
     const StTensor *qc = need(w, p + "q.conv", &st), *kc = need(w, p + "k.conv", &st);
     if (!st) return st;
     if (!shaped(qc, qn, a->conv_taps) || !shaped(kc, kn, a->conv_taps)) return bad(p, "filter shapes do not fit the configuration");
@@ -125,7 +124,7 @@ base::Status VurazenModel::build_window_attention(const json::Value& c, const Sa
 
 base::Status VurazenModel::build_delta(const json::Value& c, const SafetensorsFile& w, const std::string& p, kllm_seq_delta* a) {
   a->heads = get_int(c, "heads"), a->kv_heads = get_int(c, "kv_heads"), a->dim = get_int(c, "dim"), a->vdim = get_int(c, "vdim");
-  a->conv_taps = present(c, "conv") ? get_int(c, "conv") : 1;
+  a->conv_taps = get_int(c, "conv");
   if (a->heads <= 0 || a->kv_heads <= 0 || a->heads % a->kv_heads || a->dim <= 0 || a->vdim <= 0 || a->conv_taps < 1)
     return bad(p, "bad mixer configuration");
   base::Status st;
@@ -151,8 +150,7 @@ base::Status VurazenModel::build_delta(const json::Value& c, const SafetensorsFi
   if (st = read_values(alog, a->heads, &rate); !st) return st;
   for (float& r : rate) r = std::exp(r);
   if (st = upload_values(rate, &a->rate); !st) return st;
-  a->conv_w = nullptr;
-  if (a->conv_taps > 1) {
+  {  // a filter of one tap is still a weight per channel
     const StTensor *qc = need(w, p + "q.conv", &st), *kc = need(w, p + "k.conv", &st), *vc = need(w, p + "v.conv", &st);
     if (!st) return st;
     if (!shaped(qc, qn, a->conv_taps) || !shaped(kc, qn, a->conv_taps) || !shaped(vc, vn, a->conv_taps))
@@ -229,8 +227,8 @@ base::Status VurazenModel::check_folder(const json::Value& config, const Safeten
     } else if (type == "lightning") {
       for (const char* n : {"q", "k", "v", "g", "norm", "o"}) names.push_back(std::string("mix.") + n);
     } else if (type == "parallel") {
-      for (const char* n : {"q", "q.b", "k", "k.b", "sink", "o"}) names.push_back(std::string("mix.left.") + n);
-      for (const char* n : {"q", "k", "v", "b", "A_log", "norm", "a1", "a2", "dt_bias", "g1", "g2", "o"})
+      for (const char* n : {"q", "q.b", "q.conv", "k", "k.b", "k.conv", "sink", "o"}) names.push_back(std::string("mix.left.") + n);
+      for (const char* n : {"q", "q.conv", "k", "k.conv", "v", "v.conv", "b", "A_log", "norm", "a1", "a2", "dt_bias", "g1", "g2", "o"})
         names.push_back(std::string("mix.right.") + n);
     } else {
       return base::error::FunctionNotImplement("layer " + std::to_string(i) + ": unknown mixer '" + type + "'");
