@@ -138,10 +138,10 @@ typedef struct kllm_seq_delta {
   int32_t heads, kv_heads, dim, vdim, conv_taps, decay_rank, gate_rank;
   const void* w_in;        /* [2 * kv_heads*dim + heads*vdim + heads + decay_rank + gate_rank, width]: q | k | v | beta | a1 | g1 rows */
   const float* conv_w;     /* [2 * kv_heads*dim + heads*vdim][conv_taps] fp32 */
-  const float* w_a2;       /* [heads*dim, decay_rank] fp32 */
+  const void* w_low2;      /* [heads*dim + heads*vdim, decay_rank + gate_rank], compute type: the two second low-rank
+                              projections as one product, W_a2 in the upper left block, W_g2 in the lower right, zeros elsewhere */
   const float* dt_bias;    /* [heads*dim] */
   const float* rate;       /* [heads] fp32: exp(A_log) */
-  const float* w_g2;       /* [heads*vdim, gate_rank] fp32 */
   const float* out_norm_w; /* [vdim] */
   const void* w_out;       /* [width, heads*vdim] */
 } kllm_seq_delta;

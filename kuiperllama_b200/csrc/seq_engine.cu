@@ -120,7 +120,7 @@ struct kllm_seq_engine {
   DevBuf lat_c, lat_kr, lat_kp, lat_vp, lat_q, lat_k, lat_v;  // a prompt step's latents expanded into per-head keys / values
   DevBuf x0, hn, qf, qa, ol;  // embedding output; fp32 normed rows ahead of a token shift; latent / linear attention scratch
   DevBuf y3, y4;              // outputs of a second mixer and of a feed-forward that runs beside the mixer
-  DevBuf rec_a, rec_b;        // fp32 scratch of the selective scan (filtered rows, low-rank rows) and the delta rule (prepared rows)
+  DevBuf rec_a, rec_b, rec_c; // fp32 scratch of the selective scan (filtered rows, low-rank rows) and the delta rule (prepared rows)
   float* logits_pinned = nullptr;
   size_t logits_pinned_cap = 0;
   float* trace_host = nullptr;
@@ -152,7 +152,7 @@ struct kllm_seq_engine {
   }
   // limits over the layers
   int max_proj = 0, max_q = 0, max_att = 0, max_heads = 0, max_top = 0, max_ff = 0, max_sff = 0;
-  int max_qf = 0, max_qa = 0, max_ol = 0, max_rec_a = 0, max_rec_b = 0;
+  int max_qf = 0, max_qa = 0, max_ol = 0, max_rec_a = 0, max_rec_b = 0, max_rec_c = 0;
   bool any_mixer2 = false, any_parallel_ff = false;
   bool any_shift = false, any_run_embed = false;
   std::vector<int32_t> run_embed;
@@ -210,10 +210,10 @@ static int validate_mixer(const kllm_seq_layer& L, int kind) {
   } else if (kind == KLLM_SEQ_MIXER_DELTA) {
     const kllm_seq_delta& a = L.delta;
     if (a.heads <= 0 || a.kv_heads <= 0 || a.heads % a.kv_heads || a.dim <= 0 || a.vdim <= 0 || a.conv_taps < 1 ||
-        a.decay_rank <= 0 || a.gate_rank <= 0 || !a.w_in || !a.w_a2 || !a.dt_bias ||
-        !a.rate || !a.w_g2 || !a.out_norm_w || !a.w_out)
+        a.decay_rank <= 0 || a.gate_rank <= 0 || !a.w_in || !a.w_low2 || !a.dt_bias ||
+        !a.rate || !a.out_norm_w || !a.w_out)
       return KLLM_E_INVALID;
-    if (a.dim > 1024) return KLLM_E_UNSUPPORTED;
+    if (a.dim > 256) return KLLM_E_UNSUPPORTED;
   } else {
     return KLLM_E_UNSUPPORTED;
   }
@@ -382,6 +382,8 @@ extern "C" int kllm_seq_create(const kllm_seq_desc* desc, void* stream, kllm_seq
         e->max_att = std::max(e->max_att, a.heads * a.vdim);
         e->max_rec_a = std::max(e->max_rec_a, delta_prep_row(a));
         e->max_rec_b = std::max(e->max_rec_b, a.heads * a.vdim);
+        e->max_rec_c = std::max(e->max_rec_c, a.heads * (a.dim + a.vdim));
+        e->max_q = std::max(e->max_q, a.decay_rank + a.gate_rank);
       }
     }
     if (L.ff_kind == KLLM_SEQ_FF_DENSE) {
@@ -567,6 +569,7 @@ extern "C" int kllm_seq_step(kllm_seq_engine* e, int32_t n_entries, const int32_
   if (e->any_parallel_ff) RC(e->y4.reserve(Ts * W * 4));
   if (e->max_rec_a > 0) RC(e->rec_a.reserve(Ts * e->max_rec_a * 4));
   if (e->max_rec_b > 0) RC(e->rec_b.reserve(Ts * e->max_rec_b * 4));
+  if (e->max_rec_c > 0) RC(e->rec_c.reserve(Ts * e->max_rec_c * 4));
   size_t ws_bytes = 0;
   for (const kllm_seq_layer& L : e->layers)
     for (int kind : {L.mixer_kind, L.mixer2_kind}) {
@@ -757,7 +760,11 @@ extern "C" int kllm_seq_step(kllm_seq_engine* e, int32_t n_entries, const int32_
       const int n_proj = 2 * A.kv_heads * A.dim + A.heads * A.vdim + A.heads + A.decay_rank + A.gate_rank;
       RC(gemm(dtype, e->h.p, A.w_in, proj, T, W, n_proj, st));
       e->mark(KLLM_SEQ_PHASE_IN_PROJ);
-      RC(launch_delta_prepare(A, proj, e->delta_conv[r], step_rows, prep, T, st));
+      // the second low-rank projections of the decays and the gates: one product on the low-rank rows in the compute type
+      float* low2 = static_cast<float*>(e->rec_c.p);
+      RC(launch_delta_low(dtype, A, proj, e->q.p, T, st));
+      RC(gemm(dtype, e->q.p, A.w_low2, low2, T, A.decay_rank + A.gate_rank, A.heads * (A.dim + A.vdim), st));
+      RC(launch_delta_prepare(A, proj, low2, e->delta_conv[r], step_rows, prep, T, st));
       e->mark(KLLM_SEQ_PHASE_QK_PREPARE);
       RC(launch_delta_rule(A, prep, e->delta_state[r], step_rows, d_eseq, max_count, o, st));
       RC(launch_delta_out(dtype, A, o, prep, d.norm_eps, e->att.p, T, st));

@@ -274,13 +274,17 @@ int launch_ssm_conv(int dtype, const kllm_seq_ssm& m, const float* uz, float* co
 int launch_ssm_scan(int dtype, const kllm_seq_ssm& m, const float* uz, const float* uc, const float* low, float* state,
                     const StepRows& rows, const int32_t* ent_seq, int max_count, void* out, cudaStream_t s);
 
-// proj [T, 2*kv_heads*dim + heads*vdim + heads + decay_rank + gate_rank] fp32 -> prep [T, delta_prep_row()] fp32:
-// q | k (unit vectors, q scaled) | v | beta | decay [heads*dim] | gate [heads*vdim]
+// proj [T, 2*kv_heads*dim + heads*vdim + heads + decay_rank + gate_rank] fp32 (q | k | v | beta | low-rank rows).
+// delta_low: the low-rank rows in the compute type [T, decay_rank + gate_rank], the input of the product with w_low2 whose
+// output is low2 [T, heads*dim + heads*vdim] fp32.
+// delta_prepare: -> prep [T, delta_prep_row()] fp32: q | k (unit vectors, q scaled) | v | decay [heads*dim] |
+// gate [heads*vdim] | beta [heads] (padded to a multiple of 4 floats)
 __host__ __device__ inline int delta_prep_row(const kllm_seq_delta& m) {
-  return 2 * m.kv_heads * m.dim + m.heads * m.vdim + m.heads + m.heads * m.dim + m.heads * m.vdim;
+  return (2 * m.kv_heads * m.dim + 2 * m.heads * m.vdim + m.heads * m.dim + m.heads + 3) & ~3;
 }
-int launch_delta_prepare(const kllm_seq_delta& m, const float* proj, float* conv_state, const StepRows& rows, float* prep, int T,
-                         cudaStream_t s);
+int launch_delta_low(int dtype, const kllm_seq_delta& m, const float* proj, void* low, int T, cudaStream_t s);
+int launch_delta_prepare(const kllm_seq_delta& m, const float* proj, const float* low2, float* conv_state, const StepRows& rows,
+                         float* prep, int T, cudaStream_t s);
 // the recurrence of every entry from its sequence's state ([slots][heads][dim][vdim] fp32); o [T, heads*vdim] fp32
 int launch_delta_rule(const kllm_seq_delta& m, const float* prep, float* state, const StepRows& rows, const int32_t* ent_seq,
                       int max_count, float* o, cudaStream_t s);

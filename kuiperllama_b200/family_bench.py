@@ -1,6 +1,7 @@
-"""`bench.py --family fobolorn`: prefill and decode throughput of the Fobolorn family (sequence-batch engine) at sizes
-that resemble a real model's layers, random weights, beside the closest existing model -- the Llama family of the
-single-sequence decoder -- at equal width, heads, active feed-forward size and number of layer runs.
+"""`bench.py --family fobolorn | kikunex | vurazen`: prefill and decode throughput of a batched family (sequence-batch
+engine) at sizes that resemble a real model's layers, random weights, beside the closest existing model at equal width,
+heads, active feed-forward size and number of layer runs: Fobolorn beside the Llama family of the single-sequence decoder,
+Kikunex beside Fobolorn, Vurazen beside Kikunex.
 
 What is timed.  A step is the call a server makes: kllm_seq_step() with token ids in host memory and the greedy ids
 read back to host memory, blocking -- so every number here is end to end.  Between timed steps a buffer larger than
@@ -18,7 +19,7 @@ import statistics
 import time
 from pathlib import Path
 
-from .sequence import BF16, F32, FobolornShape, KikunexShape, SeqEngine, load_seq_library
+from .sequence import BF16, F32, FobolornShape, KikunexShape, SeqEngine, VurazenShape, load_seq_library
 
 ROOT = Path(__file__).resolve().parent.parent
 
@@ -39,6 +40,68 @@ KIKUNEX_SIZES = {
     "m": KikunexShape("kikunex-m", 2048, 32000, _KP, (1, 3, 2), 16, 128, 64, 128, 768, 256, 512, 16, 128, 128, 4096, 32, 4, 768),
     "debug": KikunexShape("kikunex-debug", 256, 4096, _KP[:3], (1, 3, 2), 4, 32, 16, 32, 96, 64, 96, 4, 32, 32, 512, 8, 2, 128),
 }
+
+
+_VP = (("mamba", "dense"), ("parallel", "moe"), ("lightning", "moe"), ("parallel", "moe"))
+VURAZEN_SIZES = {
+    # the sizes of KIKUNEX_SIZES, layer for layer: same width, experts and layer runs; a selective scan of twice the width
+    # with 16 states, window attention of the same heads over 4 key heads (window 512, 4 kept tokens) beside a delta rule
+    # with square states, the same linear attention, gated dense layers and experts with a shared expert
+    "s": VurazenShape("vurazen-s", 1024, 32000, _VP, (1, 3, 2), 2048, 16, 64, 16, 64, 64, 16, 4, 64, 512, 4, 32,
+                      16, 16, 64, 64, 64, 2048, 16, 2, 512, 1024),
+    "m": VurazenShape("vurazen-m", 2048, 32000, _VP, (1, 3, 2), 4096, 16, 128, 16, 128, 128, 16, 4, 128, 512, 4, 64,
+                      16, 16, 128, 128, 128, 4096, 32, 4, 768, 2048),
+    "debug": VurazenShape("vurazen-debug", 256, 4096, _VP[:3], (1, 3, 2), 512, 8, 16, 4, 32, 32, 4, 2, 32, 96, 2, 16,
+                          4, 2, 32, 32, 16, 512, 8, 2, 128, 256),
+}
+
+
+def vurazen_costs(shape, prompt_len):
+    """FLOPs of a prompt step by phase class of the engine's profile."""
+    W, T = shape.width, prompt_len
+    runs = [shape.pattern[i] for i, _, _ in shape.run_order()]
+    n = {k: sum(1 for m, _ in runs if m == k) for k in ("mamba", "lightning", "parallel")}
+    win = min(shape.window, T)
+    pairs = T * win - win * (win - 1) / 2 + max(0, T - win) * shape.keep_first
+    attn_left = 2 * pairs * shape.heads * 2 * shape.dim
+    # per token and head of the delta rule: decay, prediction, update and read-out over a dim x vdim state; its low-rank
+    # decay and gate projections; per token and channel of the scan: the step size and 3 multiply-adds per state
+    attn_right = T * shape.d_heads * (8 * shape.d_dim * shape.d_vdim + 2 * shape.d_rank * (shape.d_dim + shape.d_vdim))
+    attn_scan = T * shape.inner * (2 * shape.dt_rank + 6 * shape.state)
+    chunk = 32
+    attn_lin = 2 * T * shape.lin_heads * (chunk / 2 * (shape.lin_dim + shape.lin_vdim) + 2 * shape.lin_dim * shape.lin_vdim)
+    lin_in = 2 * shape.lin_heads * (shape.lin_dim + shape.lin_vdim)
+    par_in = (shape.heads + shape.kv_heads) * shape.dim + shape.delta_in()
+    moe_runs = sum(1 for _, f in runs if f == "moe")
+    return {"in_proj": 2 * T * W * (n["mamba"] * 2 * shape.inner + n["lightning"] * lin_in + n["parallel"] * par_in),
+            "qk_prepare": 2 * T * n["mamba"] * (shape.dt_rank + 2 * shape.state) * shape.inner,
+            "attention": n["parallel"] * (attn_left + attn_right) + n["mamba"] * attn_scan + n["lightning"] * attn_lin,
+            "out_proj": 2 * T * W * (n["mamba"] * shape.inner + n["lightning"] * shape.lin_heads * shape.lin_vdim +
+                                     n["parallel"] * (shape.heads * shape.dim + shape.d_heads * shape.d_vdim)),
+            "experts": 2 * T * sum(3 * shape.dense_ff * W if f == "dense" else shape.top * 3 * shape.ff * W if f == "moe" else 0
+                                   for _, f in runs),
+            "shared": 2 * T * moe_runs * 3 * shape.shared_ff * W,
+            "head": 2 * shape.vocab * W}
+
+
+def vurazen_decode_bytes(shape, B, ctx, es):
+    """Bytes a decode step must move, by phase class: weights once per step, states read and written, the window's keys."""
+    W = shape.width
+    runs = [shape.pattern[i] for i, _, _ in shape.run_order()]
+    state = shape.state_bytes_per_step(B, ctx, es)
+    lin_in = 2 * shape.lin_heads * (shape.lin_dim + shape.lin_vdim)
+    par_in = (shape.heads + shape.kv_heads) * shape.dim + shape.delta_in()
+    n_in = {"mamba": 2 * shape.inner, "lightning": lin_in, "parallel": par_in}
+    n_out = {"mamba": shape.inner, "lightning": shape.lin_heads * shape.lin_vdim,
+             "parallel": shape.heads * shape.dim + shape.d_heads * shape.d_vdim}
+    pairs = min(B * shape.top, shape.experts)
+    return {"in_proj": sum(n_in[m] for m, _ in runs) * W * es,
+            "qk_prepare": sum((shape.dt_rank + 2 * shape.state) * shape.inner * es for m, _ in runs if m == "mamba"),
+            "out_proj": sum(n_out[m] for m, _ in runs) * W * es,
+            "experts": sum(3 * shape.dense_ff * W if f == "dense" else pairs * 3 * shape.ff * W if f == "moe" else 0
+                           for _, f in runs) * es,
+            "shared": sum(3 * shape.shared_ff * W for _, f in runs if f == "moe") * es,
+            "attention": state, "head": shape.vocab * W * es}
 
 
 def kikunex_costs(shape, prompt_len):
@@ -137,7 +200,8 @@ def bench_engine(torch, shape, dtype, prompt_len, ctx, batches, steps, warm, flu
     eng.close_seq(s)
     sec = statistics.median(times)
     kiku = isinstance(shape, KikunexShape)
-    phase_flops = kikunex_costs(shape, prompt_len) if kiku else fobolorn_costs(shape, prompt_len)
+    vura = isinstance(shape, VurazenShape)
+    phase_flops = (vurazen_costs if vura else kikunex_costs if kiku else fobolorn_costs)(shape, prompt_len)
     flops = sum(phase_flops.values())
     out["prefill"] = {"tokens": prompt_len, "tok_s": prompt_len / sec, "ms": sec * 1e3, "launches": launches,
                       "tflops": flops / sec / 1e12, "frac_of_bf16_peak": flops / sec / 1e12 / tf if dtype == BF16 else None,
@@ -167,6 +231,15 @@ def bench_engine(torch, shape, dtype, prompt_len, ctx, batches, steps, warm, flu
         # bytes a step must read: the active weights (distinct experts per token, an upper bound when tokens share
         # experts) and the cached keys / values
         W = shape.width
+        if vura:
+            phase_bytes = vurazen_decode_bytes(shape, B, ctx, es)
+            bytes_step = shape.weight_elems_per_step(B) * es + phase_bytes["attention"]
+            out["decode"][str(B)] = {
+                "batch": B, "context": ctx, "tok_s": B / sec, "ms_per_step": sec * 1e3, "launches": launches,
+                "bytes_per_step": bytes_step, "frac_of_hbm_peak": bytes_step / sec / 1e9 / hbm, "phase_ms": ph,
+                "phase_frac_of_hbm_peak": {k: (v / (ph[k] * 1e-3) / 1e9 / hbm if ph.get(k, 0) > 0 else None)
+                                           for k, v in phase_bytes.items()}}
+            continue
         if kiku:
             runs = [shape.pattern[i] for i, _, _ in shape.run_order()]
             state = shape.state_bytes_per_step(B, ctx, es)
@@ -306,6 +379,8 @@ def run(args, emit):
     steps, warm = max(3, min(args.steps, 16)), max(3, min(args.warmup, 8))
     if args.family == "kikunex":
         return run_kikunex(args, emit, torch, sizes, steps, warm, flush, hbm, tf, src)
+    if args.family == "vurazen":
+        return run_vurazen(args, emit, torch, sizes, steps, warm, flush, hbm, tf, src)
     line = {"family": "fobolorn", "metric": "prefill_and_decode_tokens_per_s", "n_gpus": 1, "steps": steps, "warmup": warm,
             "data": "synthetic", "peaks": {"hbm_gbs": hbm, "bf16_tflops": tf, "source": src},
             "config": {"l2": "a 256 MiB buffer is written between timed steps", "timing": "wall clock around the blocking "
@@ -337,6 +412,27 @@ def run_kikunex(args, emit, torch, sizes, steps, warm, flush, hbm, tf, src):
         entry = {"shape": {k: v for k, v in shape.__dict__.items()} | {"runs": shape.runs}, "kikunex": [], "closest": []}
         for dtype in (BF16, F32):
             entry["kikunex"].append(bench_engine(torch, shape, dtype, prompt, ctx, [1, 8], steps, warm, flush, hbm, tf))
+            entry["closest"].append(bench_engine(torch, close, dtype, prompt, ctx, [1, 8], steps, warm, flush, hbm, tf))
+        entry["closest_model"] = close.name
+        line["sizes"][name] = entry
+    emit(line)
+
+
+def run_vurazen(args, emit, torch, sizes, steps, warm, flush, hbm, tf, src):
+    """Vurazen beside its closest existing model, Kikunex (the same engine: linear attention, a windowed softmax
+    attention, routed experts, a loop), at equal width, heads, experts and layer runs: whole steps end to end, and the
+    engine's phase classes side by side."""
+    line = {"family": "vurazen", "metric": "prefill_and_decode_tokens_per_s", "n_gpus": 1, "steps": steps, "warmup": warm,
+            "data": "synthetic", "peaks": {"hbm_gbs": hbm, "bf16_tflops": tf, "source": src},
+            "config": {"l2": "a 256 MiB buffer is written between timed steps", "timing": "wall clock around the blocking "
+                       "step call (token ids from host memory, greedy ids back to host memory); phases by CUDA events"},
+            "sizes": {}}
+    for name in sizes:
+        shape, close = VURAZEN_SIZES[name], KIKUNEX_SIZES[name]
+        ctx, prompt = (256, 512) if name == "debug" else (1024, 2048)
+        entry = {"shape": {k: v for k, v in shape.__dict__.items()} | {"runs": shape.runs}, "vurazen": [], "closest": []}
+        for dtype in (BF16, F32):
+            entry["vurazen"].append(bench_engine(torch, shape, dtype, prompt, ctx, [1, 8], steps, warm, flush, hbm, tf))
             entry["closest"].append(bench_engine(torch, close, dtype, prompt, ctx, [1, 8], steps, warm, flush, hbm, tf))
         entry["closest_model"] = close.name
         line["sizes"][name] = entry

@@ -81,6 +81,8 @@ class SequenceModel : public base::NoCopyable {
   const StTensor* need(const SafetensorsFile& f, const std::string& name, base::Status* status) const;
   // host values as fp32 on the device
   base::Status upload_values(const std::vector<float>& values, const float** device);
+  // host values in the compute type on the device (bf16: rounded to nearest even)
+  base::Status upload_compute_values(const std::vector<float>& values, const void** device);
   // a tensor that holds ONE number, repeated `numel` times on the device (a norm whose weight is a single number)
   base::Status upload_broadcast(const StTensor* t, int64_t numel, const float** device);
   // the values of a small tensor on the host, checked against `numel`

@@ -85,6 +85,23 @@ base::Status SequenceModel::upload_values(const std::vector<float>& values, cons
   return base::error::Success();
 }
 
+base::Status SequenceModel::upload_compute_values(const std::vector<float>& values, const void** device) {
+  if (compute_ != ComputeType::kBFloat16) {
+    const float* p = nullptr;
+    base::Status st = upload_values(values, &p);
+    *device = p;
+    return st;
+  }
+  std::vector<uint16_t> half(values.size());
+  for (size_t i = 0; i < values.size(); ++i) half[i] = float_to_bf16(values[i]);
+  auto buf = device_alloc(half.size() * 2);
+  if (!buf) return base::error::InternalError("device allocation failed");
+  if (!half.empty() && cudaMemcpy(buf->ptr(), half.data(), half.size() * 2, cudaMemcpyHostToDevice) != cudaSuccess)
+    return base::error::InternalError("weight upload failed");
+  *device = buf->ptr();
+  return base::error::Success();
+}
+
 base::Status SequenceModel::read_values(const StTensor* t, int64_t numel, std::vector<float>* out) const {
   if (t == nullptr) return base::error::ModelParseError("a tensor is missing");
   if (t->numel() != numel) return base::error::ModelParseError("a tensor has an unexpected size");

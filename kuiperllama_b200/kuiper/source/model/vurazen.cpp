@@ -142,9 +142,19 @@ base::Status VurazenModel::build_delta(const json::Value& c, const SafetensorsFi
     return bad(p, "tensor shapes do not fit the configuration");
   if (st = upload_compute({q, k, v, b, a1, g1}, width_, &a->w_in); !st) return st;
   if (st = upload_compute({o}, vn, &a->w_out); !st) return st;
-  if (st = upload_f32(a2, dn * a->decay_rank, &a->w_a2); !st) return st;
+  {  // both second low-rank projections as one product: W_a2 upper left, W_g2 lower right
+    std::vector<float> wa, wg;
+    if (st = read_values(a2, dn * a->decay_rank, &wa); !st) return st;
+    if (st = read_values(g2, vn * a->gate_rank, &wg); !st) return st;
+    const int64_t cols = int64_t(a->decay_rank) + a->gate_rank;
+    std::vector<float> both(static_cast<size_t>((dn + vn) * cols), 0.f);
+    for (int64_t r = 0; r < dn; ++r)
+      for (int64_t c = 0; c < a->decay_rank; ++c) both[r * cols + c] = wa[r * a->decay_rank + c];
+    for (int64_t r = 0; r < vn; ++r)
+      for (int64_t c = 0; c < a->gate_rank; ++c) both[(dn + r) * cols + a->decay_rank + c] = wg[r * a->gate_rank + c];
+    if (st = upload_compute_values(both, &a->w_low2); !st) return st;
+  }
   if (st = upload_f32(dtb, dn, &a->dt_bias); !st) return st;
-  if (st = upload_f32(g2, vn * a->gate_rank, &a->w_g2); !st) return st;
   if (st = upload_f32(norm, a->vdim, &a->out_norm_w); !st) return st;
   std::vector<float> rate;
   if (st = read_values(alog, a->heads, &rate); !st) return st;

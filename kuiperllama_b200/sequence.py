@@ -64,7 +64,7 @@ class Ssm(ctypes.Structure):
 class Delta(ctypes.Structure):
     _fields_ = [("heads", c_int32), ("kv_heads", c_int32), ("dim", c_int32), ("vdim", c_int32), ("conv_taps", c_int32),
                 ("decay_rank", c_int32), ("gate_rank", c_int32), ("w_in", c_void_p), ("conv_w", c_void_p),
-                ("w_a2", c_void_p), ("dt_bias", c_void_p), ("rate", c_void_p), ("w_g2", c_void_p),
+                ("w_low2", c_void_p), ("dt_bias", c_void_p), ("rate", c_void_p),
                 ("out_norm_w", c_void_p), ("w_out", c_void_p)]
 
 
@@ -561,12 +561,18 @@ class SeqEngine:
                 Cd = 2 * shape.d_kv_heads * shape.d_dim + shape.d_heads * shape.d_vdim
                 b.w_in = rnd(shape.delta_in(), W, std=W ** -0.5).data_ptr()
                 b.conv_w = f32(Cd, shape.taps, std=0.5).data_ptr()
-                b.w_a2 = f32(shape.d_heads * shape.d_dim, shape.d_rank, std=shape.d_rank ** -0.5).data_ptr()
+                low2 = torch.zeros(shape.d_heads * (shape.d_dim + shape.d_vdim), 2 * shape.d_rank, device="cuda")
+                low2[:shape.d_heads * shape.d_dim, :shape.d_rank] = torch.randn(
+                    shape.d_heads * shape.d_dim, shape.d_rank, device="cuda", generator=g) * shape.d_rank ** -0.5
+                low2[shape.d_heads * shape.d_dim:, shape.d_rank:] = torch.randn(
+                    shape.d_heads * shape.d_vdim, shape.d_rank, device="cuda", generator=g) * shape.d_rank ** -0.5
+                low2 = low2.to(td).contiguous()
+                keep.append(low2)
+                b.w_low2 = low2.data_ptr()
                 b.dt_bias = f32(shape.d_heads * shape.d_dim, std=0.5, mean=-2.0).data_ptr()
                 rate = torch.rand(shape.d_heads, device="cuda", generator=g) * 2.0 + 0.02
                 keep.append(rate)
                 b.rate = rate.data_ptr()
-                b.w_g2 = f32(shape.d_heads * shape.d_vdim, shape.d_rank, std=shape.d_rank ** -0.5).data_ptr()
                 b.out_norm_w = f32(shape.d_vdim, std=0.05, mean=1.0).data_ptr()
                 b.w_out = rnd(W, shape.d_heads * shape.d_vdim, std=(shape.d_heads * shape.d_vdim) ** -0.5).data_ptr()
             L.ff_kind = {None: 0, "moe": 1, "dense": 2}[ff]
