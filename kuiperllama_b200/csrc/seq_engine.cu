@@ -582,6 +582,9 @@ extern "C" int kllm_seq_step(kllm_seq_engine* e, int32_t n_entries, const int32_
   for (const kllm_seq_layer& L : e->layers)  // the chunk sums of linear attention share the attention workspace
     if (L.mixer_kind == KLLM_SEQ_MIXER_LINEAR || L.mixer2_kind == KLLM_SEQ_MIXER_LINEAR)
       ws_bytes = std::max(ws_bytes, linear_attention_scratch_bytes(L.linear.heads, L.linear.dim, L.linear.vdim, T, n_entries, max_count));
+  for (const kllm_seq_layer& L : e->layers)  // and so do the segments of the selective scan
+    if (L.mixer_kind == KLLM_SEQ_MIXER_SSM || L.mixer2_kind == KLLM_SEQ_MIXER_SSM)
+      ws_bytes = std::max(ws_bytes, ssm_scan_scratch_bytes(L.ssm, T, n_entries, max_count));
   RC(e->ws.reserve(ws_bytes));
   const bool grouped = T >= kGroupedMinTokens;
   if (e->max_top > 0) {
@@ -749,7 +752,8 @@ extern "C" int kllm_seq_step(kllm_seq_engine* e, int32_t n_entries, const int32_
       RC(launch_ssm_conv(dtype, A, proj, e->ssm_conv[r], step_rows, uc, e->att.p, T, st));
       RC(gemm(dtype, e->att.p, A.w_x, low, T, A.inner, A.dt_rank + 2 * A.state, st));
       e->mark(KLLM_SEQ_PHASE_QK_PREPARE);
-      RC(launch_ssm_scan(dtype, A, proj, uc, low, e->ssm_state[r], step_rows, d_eseq, max_count, e->att.p, st));
+      RC(launch_ssm_scan(dtype, A, proj, uc, low, e->ssm_state[r], step_rows, d_eseq, max_count, T,
+                         static_cast<float*>(e->ws.p), e->att.p, st));
       e->mark(KLLM_SEQ_PHASE_ATTENTION);
       RC(gemm(dtype, e->att.p, A.w_out, yout, T, A.inner, W, st));
       e->mark(KLLM_SEQ_PHASE_OUT_PROJ);

@@ -271,8 +271,11 @@ int launch_ssm_conv(int dtype, const kllm_seq_ssm& m, const float* uz, float* co
                     void* uc_ct, int T, cudaStream_t s);
 // the scan over every entry from its sequence's state ([slots][inner][state] fp32, zeros at position 0):
 // out[t] = y[t] * silu(z[t]) in the compute type
+// Steps with long entries scan segments of an entry in parallel through `scratch` (ssm_scan_scratch_bytes(); 0: not needed).
+size_t ssm_scan_scratch_bytes(const kllm_seq_ssm& m, int T, int n_entries, int max_count);
 int launch_ssm_scan(int dtype, const kllm_seq_ssm& m, const float* uz, const float* uc, const float* low, float* state,
-                    const StepRows& rows, const int32_t* ent_seq, int max_count, void* out, cudaStream_t s);
+                    const StepRows& rows, const int32_t* ent_seq, int max_count, int T, float* scratch, void* out,
+                    cudaStream_t s);
 
 // proj [T, 2*kv_heads*dim + heads*vdim + heads + decay_rank + gate_rank] fp32 (q | k | v | beta | low-rank rows).
 // delta_low: the low-rank rows in the compute type [T, decay_rank + gate_rank], the input of the product with w_low2 whose

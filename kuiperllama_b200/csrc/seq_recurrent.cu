@@ -88,10 +88,12 @@ __device__ __forceinline__ float conv_at(const float* __restrict__ in, int strid
 }
 
 // The state after the entry: row i = the input at position end - hist + i.  In place: row i only reads old rows >= i.
+// Channels c0 .. c0 + n - 1 only (the CTA's own).
 __device__ __forceinline__ void conv_state_write(const float* __restrict__ in, int stride, int C, int taps,
-                                                 const float* __restrict__ bias, float* __restrict__ st, const RowPlace& p) {
+                                                 const float* __restrict__ bias, float* __restrict__ st, const RowPlace& p,
+                                                 int c0, int n) {
   const int hist = taps - 1, end = p.pos0 + p.count;
-  for (int c = threadIdx.x; c < C; c += blockDim.x) {
+  for (int c = c0 + threadIdx.x; c < c0 + n; c += blockDim.x) {
     const float b = bias ? bias[c] : 0.f;
     for (int i = 0; i < hist; ++i) {
       const int sp = end - hist + i;
@@ -110,26 +112,28 @@ __device__ __forceinline__ AT* page_row(AT* base, const PagedKV& kv, int seq, in
   return base + (static_cast<size_t>(page) * kv.page + pos % kv.page) * row;
 }
 
+// One CTA per (row, query or key head): unit u < heads is query head u, the others are the key heads.
 template <typename AT>
 __global__ void qk_conv_prepare_kernel(AttnShape a, AttnPrep pr, const float* __restrict__ qk, StepRows rows,
                                        AT* __restrict__ q, PagedKV kv) {
-  extern __shared__ float cs[];  // [C] the filtered row
+  extern __shared__ float cs[];  // [dim] the head's filtered row
   const RowPlace p = place_row(rows, blockIdx.x, pr.taps);
   if (p.n_here == 0) return;
-  const int qn = a.heads * a.dim, C = qn + a.kv_heads * a.dim, hist = pr.taps - 1;
+  const int u = blockIdx.y;
+  const bool is_q = u < a.heads;
+  const int qn = a.heads * a.dim, C = qn + a.kv_heads * a.dim, hist = pr.taps - 1, c0 = u * a.dim;
   float* st = hist > 0 ? pr.conv_state + static_cast<size_t>(p.seq) * hist * C : nullptr;
   const int rd = pr.rope_dims, half = rd / 2;
   for (int jj = 0; jj < p.n_here; ++jj) {
     const int t = blockIdx.x + jj, pos = p.pos0 + p.j0 + jj;
-    for (int c = threadIdx.x; c < C; c += blockDim.x) cs[c] = conv_at(qk, C, c, C, pr.taps, pr.conv_w, pr.bias, st, p, pos);
+    for (int d = threadIdx.x; d < a.dim; d += blockDim.x)
+      cs[d] = conv_at(qk, C, c0 + d, C, pr.taps, pr.conv_w, pr.bias, st, p, pos);
     __syncthreads();
-    AT* krow = page_row(static_cast<AT*>(kv.k), kv, p.seq, pos, kv.k_row);
-    AT* vrow = page_row(static_cast<AT*>(kv.v), kv, p.seq, pos, kv.v_row);
-    for (int c = threadIdx.x; c < C; c += blockDim.x) {
-      const bool is_q = c < qn;
-      const int d = (is_q ? c : c - qn) % a.dim;
-      float v = cs[c];
-      if (!is_q) vrow[c - qn] = from_f<AT>(v);  // the values: keys before the rotation
+    AT* krow = is_q ? nullptr : page_row(static_cast<AT*>(kv.k), kv, p.seq, pos, kv.k_row) + (c0 - qn);
+    AT* vrow = is_q ? nullptr : page_row(static_cast<AT*>(kv.v), kv, p.seq, pos, kv.v_row) + (c0 - qn);
+    for (int d = threadIdx.x; d < a.dim; d += blockDim.x) {
+      float v = cs[d];
+      if (!is_q) vrow[d] = from_f<AT>(v);  // the values: keys before the rotation
       if (d < rd) {
         int i, partner;
         bool lead;  // the member of the pair that becomes u cos - v sin
@@ -138,15 +142,15 @@ __global__ void qk_conv_prepare_kernel(AttnShape a, AttnPrep pr, const float* __
         const float freq = powf(pr.rope_base, -2.0f * static_cast<float>(i) / static_cast<float>(rd));
         const float ang = static_cast<float>(pos) * freq;
         const float co = cosf(ang), si = sinf(ang);
-        const float o = cs[c - d + partner];
+        const float o = cs[partner];
         v = lead ? v * co - o * si : v * co + o * si;
       }
-      if (is_q) q[static_cast<size_t>(t) * qn + c] = from_f<AT>(v);
-      else krow[c - qn] = from_f<AT>(v);
+      if (is_q) q[static_cast<size_t>(t) * qn + c0 + d] = from_f<AT>(v);
+      else krow[d] = from_f<AT>(v);
     }
     __syncthreads();
   }
-  if (p.j0 == 0 && hist > 0) conv_state_write(qk, C, C, pr.taps, pr.bias, st, p);
+  if (p.j0 == 0 && hist > 0) conv_state_write(qk, C, C, pr.taps, pr.bias, st, p, c0, a.dim);
 }
 
 // ---- selective scan ----------------------------------------------------------------------------------------------------
@@ -158,34 +162,54 @@ __global__ void ssm_conv_kernel(int inner, int taps, const float* __restrict__ c
   if (p.n_here == 0) return;
   const int hist = taps - 1;
   float* st = hist > 0 ? conv_state + static_cast<size_t>(p.seq) * hist * inner : nullptr;
+  const int c0 = blockIdx.y * blockDim.x, c = c0 + threadIdx.x;
   for (int jj = 0; jj < p.n_here; ++jj) {
     const int t = blockIdx.x + jj, pos = p.pos0 + p.j0 + jj;
-    for (int c = threadIdx.x; c < inner; c += blockDim.x) {
+    if (c < inner) {
       const float v = siluf(conv_at(uz, 2 * inner, c, inner, taps, conv_w, nullptr, st, p, pos) + (conv_b ? conv_b[c] : 0.f));
       uc[static_cast<size_t>(t) * inner + c] = v;
       uc_ct[static_cast<size_t>(t) * inner + c] = from_f<AT>(v);
     }
   }
-  if (p.j0 == 0 && hist > 0) {
-    __syncthreads();
-    conv_state_write(uz, 2 * inner, inner, taps, nullptr, st, p);
-  }
+  // the thread that read a channel's old state is the one that writes its new one
+  if (p.j0 == 0 && hist > 0) conv_state_write(uz, 2 * inner, inner, taps, nullptr, st, p, c0, min(static_cast<int>(blockDim.x), inner - c0));
 }
 
 constexpr int kScanThreads = 128;
 constexpr int kScanPerLane = 4;  // states per thread: up to 32 lanes share a channel, so state <= 128
+constexpr int kScanSeg = 128;          // rows of a segment when long entries are scanned in parallel
+constexpr int kScanParallelFrom = 256; // entries longer than this are cut into segments
+
+// Long entries.  The recurrence S_t = exp(d_t a) S_(t-1) + b_t is linear, so an entry is cut into segments of kScanSeg rows
+// that are scanned at the same time, each from an empty state (the first from the sequence's): with D_t the sum of the step
+// sizes from the segment's start to row t, the true state is S_t = S'_t + exp(a D_t) S_start, S' the segment's own scan.
+//   ssm_scan_kernel<SEGMENTS>   the segment's own scan: y' (fp32, ungated), D_t of every row, the segment's last S' and D
+//   ssm_carry_kernel            S_start of every segment, one after the other; the sequence's new state
+//   ssm_finish_kernel           y = y' + sum_n C_n exp(a_n D_t) S_start[n]; gate with silu(z); compute type
+// Scratch (fp32): y' [T][inner] | D [T][inner] | last S' (then S_start) [segments][inner][state] | last D [segments][inner].
+struct ScanScratch {
+  float* yl;
+  float* cum;
+  float* send;
+  float* cend;
+};
+__host__ __device__ inline int scan_segment_id(int first, int e, int seg) { return first / kScanSeg + e + seg; }
 
 // One CTA: one entry, CH = kScanThreads / L channels; L lanes share a channel, lane l holds its states 4l .. 4l + 3.
 // The rows of W_dt of the CTA's channels stay in shared memory.  Chunks of `chunk` rows are staged in shared memory (the
 // low-rank rows, u, z), the step sizes of the chunk are computed by all threads, then the recurrence runs over the
 // chunk's rows.
-template <typename AT>
+template <typename AT, bool SEGMENTS>
 __global__ void __launch_bounds__(kScanThreads)
 ssm_scan_kernel(kllm_seq_ssm m, int L, int chunk, const float* __restrict__ uz, const float* __restrict__ uc,
                 const float* __restrict__ low, float* __restrict__ state, StepRows rows,
-                const int32_t* __restrict__ ent_seq, AT* __restrict__ out) {
-  const int e = blockIdx.y;
-  const int first = rows.ent_first[e], count = rows.ent_count[e], pos0 = rows.ent_pos0[e], seq = ent_seq[e];
+                const int32_t* __restrict__ ent_seq, AT* __restrict__ out, ScanScratch sc) {
+  const int e = SEGMENTS ? blockIdx.z : blockIdx.y, seg = SEGMENTS ? blockIdx.y : 0;
+  const int e_first = rows.ent_first[e], e_count = rows.ent_count[e], pos0 = rows.ent_pos0[e], seq = ent_seq[e];
+  if (SEGMENTS && seg * kScanSeg >= e_count) return;
+  // the rows of this CTA: the whole entry, or one segment of it
+  const int first = SEGMENTS ? e_first + seg * kScanSeg : e_first;
+  const int count = SEGMENTS ? min(kScanSeg, e_count - seg * kScanSeg) : e_count;
   const int CH = kScanThreads / L;
   const int c0 = blockIdx.x * CH;
   const int lane = threadIdx.x % L, cl = threadIdx.x / L, c = c0 + cl;
@@ -209,10 +233,11 @@ ssm_scan_kernel(kllm_seq_ssm m, int L, int chunk, const float* __restrict__ uz, 
   for (int k = 0; k < kScanPerLane; ++k) {
     const int n = lane * kScanPerLane + k;
     const bool on = live && n < N;
-    S[k] = on && pos0 > 0 ? st[n] : 0.f;
+    S[k] = on && pos0 > 0 && seg == 0 ? st[n] : 0.f;
     A[k] = on ? m.a[static_cast<size_t>(c) * N + n] : 0.f;
   }
   const float dskip = live ? m.d[c] : 0.f;
+  float cum = 0.f;  // the sum of the step sizes since the segment's start
   for (int r0 = 0; r0 < count; r0 += chunk) {
     const int nr = min(chunk, count - r0);
     __syncthreads();
@@ -253,18 +278,90 @@ ssm_scan_kernel(kllm_seq_ssm m, int L, int chunk, const float* __restrict__ uz, 
         }
       }
       for (int o = L >> 1; o > 0; o >>= 1) y += __shfl_xor_sync(kAll, y, o);
-      if (lane == 0) y_s[r * CH + cl] = (y + dskip * u) * siluf(z_s[r * CH + cl]);
+      if (SEGMENTS) {
+        cum += dt;
+        if (lane == 0) y_s[r * CH + cl] = y + dskip * u, dt_s[r * CH + cl] = cum;  // this row's dt is no longer needed
+      } else if (lane == 0) {
+        y_s[r * CH + cl] = (y + dskip * u) * siluf(z_s[r * CH + cl]);
+      }
     }
     __syncthreads();
     for (int i = threadIdx.x; i < nr * CH; i += kScanThreads) {
       const int r = i / CH, cc = c0 + i % CH;
-      if (cc < m.inner) out[static_cast<size_t>(first + r0 + r) * m.inner + cc] = from_f<AT>(y_s[i]);
+      if (cc >= m.inner) continue;
+      const size_t at = static_cast<size_t>(first + r0 + r) * m.inner + cc;
+      if (SEGMENTS) sc.yl[at] = y_s[i], sc.cum[at] = dt_s[i];
+      else out[at] = from_f<AT>(y_s[i]);
     }
+  }
+  if (SEGMENTS) {
+    const size_t sid = scan_segment_id(e_first, e, seg);
+    if (live && lane == 0) sc.cend[sid * m.inner + c] = cum;
+    st = sc.send + (sid * m.inner + (live ? c : 0)) * N;
   }
 #pragma unroll
   for (int k = 0; k < kScanPerLane; ++k) {
     const int n = lane * kScanPerLane + k;
     if (live && n < N) st[n] = S[k];
+  }
+}
+
+// One thread per (entry, channel, state): the start state of every segment after the first, and the sequence's new state.
+__global__ void ssm_carry_kernel(kllm_seq_ssm m, float* __restrict__ state, StepRows rows, const int32_t* __restrict__ ent_seq,
+                                 ScanScratch sc) {
+  const int e = blockIdx.y;
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= m.inner * m.state) return;
+  const int first = rows.ent_first[e], count = rows.ent_count[e];
+  const int segs = (count + kScanSeg - 1) / kScanSeg;
+  const float a = m.a[i];
+  const int c = i / m.state;
+  const size_t per = static_cast<size_t>(m.inner) * m.state;
+  float carry = sc.send[scan_segment_id(first, e, 0) * per + i];  // the first segment started from the sequence's state
+  for (int sgm = 1; sgm < segs; ++sgm) {
+    const size_t sid = scan_segment_id(first, e, sgm);
+    const float own = sc.send[sid * per + i];
+    sc.send[sid * per + i] = carry;
+    carry = fmaf(expf(a * sc.cend[sid * m.inner + c]), carry, own);
+  }
+  state[static_cast<size_t>(ent_seq[e]) * per + i] = carry;
+}
+
+// One CTA: CH channels of one segment; L lanes share a channel as in the scan.  Rows are independent here.
+template <typename AT>
+__global__ void __launch_bounds__(kScanThreads)
+ssm_finish_kernel(kllm_seq_ssm m, int L, const float* __restrict__ uz, const float* __restrict__ low, StepRows rows,
+                  AT* __restrict__ out, ScanScratch sc) {
+  const int e = blockIdx.z, seg = blockIdx.y;
+  const int e_first = rows.ent_first[e], e_count = rows.ent_count[e];
+  if (seg * kScanSeg >= e_count) return;
+  const int first = e_first + seg * kScanSeg, count = min(kScanSeg, e_count - seg * kScanSeg);
+  const int CH = kScanThreads / L;
+  const int lane = threadIdx.x % L, cl = threadIdx.x / L, c = blockIdx.x * CH + cl;
+  const bool live = c < m.inner;
+  const int R = m.dt_rank, N = m.state, LW = R + 2 * N;
+  float S0[kScanPerLane], A[kScanPerLane];
+  const size_t sid = scan_segment_id(e_first, e, seg);
+#pragma unroll
+  for (int k = 0; k < kScanPerLane; ++k) {
+    const int n = lane * kScanPerLane + k;
+    const bool on = live && n < N && seg > 0;
+    S0[k] = on ? sc.send[(sid * m.inner + c) * N + n] : 0.f;
+    A[k] = on ? m.a[static_cast<size_t>(c) * N + n] : 0.f;
+  }
+  for (int r = 0; r < count; ++r) {
+    const size_t row = static_cast<size_t>(first + r);
+    float corr = 0.f;
+    if (seg > 0 && live) {
+      const float cum = sc.cum[row * m.inner + c];
+      const float* Cn = low + row * LW + R + N + lane * kScanPerLane;
+#pragma unroll
+      for (int k = 0; k < kScanPerLane; ++k)
+        if (lane * kScanPerLane + k < N) corr = fmaf(Cn[k] * expf(A[k] * cum), S0[k], corr);
+    }
+    for (int o = L >> 1; o > 0; o >>= 1) corr += __shfl_xor_sync(kAll, corr, o);
+    if (lane == 0 && live)
+      out[row * m.inner + c] = from_f<AT>((sc.yl[row * m.inner + c] + corr) * siluf(uz[row * 2 * m.inner + m.inner + c]));
   }
 }
 
@@ -287,44 +384,59 @@ __global__ void delta_low_kernel(kllm_seq_delta m, const float* __restrict__ pro
   low[i] = from_f<AT>(proj[(i / nl) * (C + m.heads + nl) + C + m.heads + i % nl]);
 }
 
-// One CTA per row (see the note on filters at the top).  Shared memory: the filtered q | k | v row.
+// One CTA per (row, head h) (see the note on filters at the top): the head's value channels, decays, gates and beta, and --
+// for h < kv_heads -- query head h and key head h.  Shared memory: the filtered q | k | v channels of the CTA.
 __global__ void delta_prepare_kernel(kllm_seq_delta m, const float* __restrict__ proj, const float* __restrict__ low2,
                                      float* __restrict__ conv_state, StepRows rows, float* __restrict__ prep) {
-  extern __shared__ float cs[];
+  extern __shared__ float cs[];  // [dim] q, [dim] k, [vdim] v
   const RowPlace p = place_row(rows, blockIdx.x, m.conv_taps);
   if (p.n_here == 0) return;
-  const int qn = m.kv_heads * m.dim, vn = m.heads * m.vdim, dn = m.heads * m.dim, C = 2 * qn + vn, hist = m.conv_taps - 1;
+  const int h = blockIdx.y;
+  const bool has_qk = h < m.kv_heads;
+  const int D = m.dim, V = m.vdim;
+  const int qn = m.kv_heads * D, vn = m.heads * V, dn = m.heads * D, C = 2 * qn + vn, hist = m.conv_taps - 1;
   const int stride = C + m.heads + m.decay_rank + m.gate_rank;
   const int prow = delta_prep_row(m);
   const DeltaRow at = delta_row(m);
   float* st = hist > 0 ? conv_state + static_cast<size_t>(p.seq) * hist * C : nullptr;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   for (int jj = 0; jj < p.n_here; ++jj) {
     const int t = blockIdx.x + jj, pos = p.pos0 + p.j0 + jj;
     const float* row = proj + static_cast<size_t>(t) * stride;
     const float* l2 = low2 + static_cast<size_t>(t) * (dn + vn);
     float* dst = prep + static_cast<size_t>(t) * prow;
-    for (int c = threadIdx.x; c < C; c += blockDim.x)
-      cs[c] = siluf(conv_at(proj, stride, c, C, m.conv_taps, m.conv_w, nullptr, st, p, pos));
+    for (int i = threadIdx.x; i < (has_qk ? 2 * D : 0) + V; i += blockDim.x) {
+      const bool is_v = !has_qk || i >= 2 * D;
+      const int c = is_v ? 2 * qn + h * V + (i - (has_qk ? 2 * D : 0)) : (i < D ? h * D + i : qn + h * D + (i - D));
+      cs[is_v ? 2 * D + (i - (has_qk ? 2 * D : 0)) : i] = siluf(conv_at(proj, stride, c, C, m.conv_taps, m.conv_w, nullptr, st, p, pos));
+    }
     __syncthreads();
-    // unit vectors: query heads, then key heads
-    for (int u = warp; u < 2 * m.kv_heads; u += nw) {
-      const float* src = cs + u * m.dim;
+    if (has_qk && warp < 2) {  // unit vectors: warp 0 the query head, warp 1 the key head
+      const float* src = cs + warp * D;
       float ss = 0.f;
-      for (int d = lane; d < m.dim; d += 32) ss = fmaf(src[d], src[d], ss);
+      for (int d = lane; d < D; d += 32) ss = fmaf(src[d], src[d], ss);
       ss = warp_sum(ss);
       float rinv = 1.0f / sqrtf(ss + 1e-6f);
-      if (u < m.kv_heads) rinv *= 1.0f / sqrtf(static_cast<float>(m.dim));
-      for (int d = lane; d < m.dim; d += 32) dst[u * m.dim + d] = src[d] * rinv;
+      if (warp == 0) rinv *= 1.0f / sqrtf(static_cast<float>(D));
+      float* out = dst + (warp == 0 ? at.q : at.k) + h * D;
+      for (int d = lane; d < D; d += 32) out[d] = src[d] * rinv;
     }
-    for (int i = threadIdx.x; i < vn; i += blockDim.x) dst[at.v + i] = cs[2 * qn + i];
-    for (int h = threadIdx.x; h < m.heads; h += blockDim.x) dst[at.beta + h] = sigmoidf(row[C + h]);
-    for (int i = threadIdx.x; i < dn; i += blockDim.x)
-      dst[at.decay + i] = expf(-m.rate[i / m.dim] * softplusf(l2[i] + m.dt_bias[i]));
-    for (int i = threadIdx.x; i < vn; i += blockDim.x) dst[at.gate + i] = sigmoidf(l2[dn + i]);
+    for (int i = threadIdx.x; i < V; i += blockDim.x) {
+      dst[at.v + h * V + i] = cs[2 * D + i];
+      dst[at.gate + h * V + i] = sigmoidf(l2[dn + h * V + i]);
+    }
+    if (threadIdx.x == 0) dst[at.beta + h] = sigmoidf(row[C + h]);
+    for (int i = threadIdx.x; i < D; i += blockDim.x)
+      dst[at.decay + h * D + i] = expf(-m.rate[h] * softplusf(l2[h * D + i] + m.dt_bias[h * D + i]));
     __syncthreads();
   }
-  if (p.j0 == 0 && hist > 0) conv_state_write(proj, stride, C, m.conv_taps, nullptr, st, p);
+  if (p.j0 == 0 && hist > 0) {
+    if (has_qk) {
+      conv_state_write(proj, stride, C, m.conv_taps, nullptr, st, p, h * D, D);
+      conv_state_write(proj, stride, C, m.conv_taps, nullptr, st, p, qn + h * D, D);
+    }
+    conv_state_write(proj, stride, C, m.conv_taps, nullptr, st, p, 2 * qn + h * V, V);
+  }
 }
 
 constexpr int kDeltaThreads = 128;
@@ -510,37 +622,66 @@ int launch_qk_conv_prepare(int dtype, const AttnShape& a, const AttnPrep& p, con
                            const PagedKV& kv, int T, cudaStream_t s) {
   const int C = (a.heads + a.kv_heads) * a.dim;
   if (p.taps < 1 || (p.taps > 1 && !p.conv_state) || (p.rope_dims & 1) || p.rope_dims > a.dim) return KLLM_E_INVALID;
-  const size_t smem = static_cast<size_t>(C) * sizeof(float);
-  if (smem > 48 * 1024) return KLLM_E_UNSUPPORTED;
-  const int threads = C >= 2048 ? 512 : 256;
-  KLLM_SEQ_DISPATCH(dtype, (qk_conv_prepare_kernel<AT><<<T, threads, smem, s>>>(a, p, qk, rows, static_cast<AT*>(q), kv)));
+  (void)C;
+  const size_t smem = static_cast<size_t>(a.dim) * sizeof(float);
+  const int threads = std::min(256, (a.dim + 31) / 32 * 32);
+  const dim3 grid(T, a.heads + a.kv_heads);
+  KLLM_SEQ_DISPATCH(dtype, (qk_conv_prepare_kernel<AT><<<grid, threads, smem, s>>>(a, p, qk, rows, static_cast<AT*>(q), kv)));
   return done();
 }
 
 int launch_ssm_conv(int dtype, const kllm_seq_ssm& m, const float* uz, float* conv_state, const StepRows& rows, float* uc,
                     void* uc_ct, int T, cudaStream_t s) {
-  const int threads = m.inner >= 2048 ? 512 : 256;
-  KLLM_SEQ_DISPATCH(dtype, (ssm_conv_kernel<AT><<<T, threads, 0, s>>>(m.inner, m.conv_taps, m.conv_w, m.conv_b, uz, conv_state,
+  const int threads = 256;
+  const dim3 grid(T, (m.inner + threads - 1) / threads);
+  KLLM_SEQ_DISPATCH(dtype, (ssm_conv_kernel<AT><<<grid, threads, 0, s>>>(m.inner, m.conv_taps, m.conv_w, m.conv_b, uz, conv_state,
                                                                      rows, uc, static_cast<AT*>(uc_ct))));
   return done();
 }
 
+size_t ssm_scan_scratch_bytes(const kllm_seq_ssm& m, int T, int n_entries, int max_count) {
+  if (max_count <= kScanParallelFrom) return 0;
+  const size_t segs = static_cast<size_t>(T) / kScanSeg + n_entries + 1;
+  return (2 * static_cast<size_t>(T) * m.inner + segs * m.inner * (m.state + 1)) * sizeof(float);
+}
+
 int launch_ssm_scan(int dtype, const kllm_seq_ssm& m, const float* uz, const float* uc, const float* low, float* state,
-                    const StepRows& rows, const int32_t* ent_seq, int max_count, void* out, cudaStream_t s) {
+                    const StepRows& rows, const int32_t* ent_seq, int max_count, int T, float* scratch, void* out,
+                    cudaStream_t s) {
   if (m.state > 32 * kScanPerLane) return KLLM_E_UNSUPPORTED;
   // at least 4 lanes per channel: at most 32 channels of a chunk in shared memory
   const int L = std::max(4, lanes_for(m.state, kScanPerLane));
   const int CH = kScanThreads / L;
+  const bool segments = max_count > kScanParallelFrom && scratch != nullptr;
+  const int longest = segments ? kScanSeg : max_count;
   auto smem_for = [&](int chunk) {
     return (static_cast<size_t>(CH) * (m.dt_rank + 1) + static_cast<size_t>(chunk) * (m.dt_rank + 2 * m.state) +
             4 * static_cast<size_t>(chunk) * CH) * sizeof(float);
   };
   int chunk = 32;
-  while (chunk > 1 && (smem_for(chunk) > 48 * 1024 || chunk / 2 >= max_count)) chunk /= 2;
+  while (chunk > 1 && (smem_for(chunk) > 48 * 1024 || chunk / 2 >= longest)) chunk /= 2;
   if (smem_for(chunk) > 48 * 1024) return KLLM_E_UNSUPPORTED;
-  const dim3 grid((m.inner + CH - 1) / CH, rows.n_entries);
-  KLLM_SEQ_DISPATCH(dtype, (ssm_scan_kernel<AT><<<grid, kScanThreads, smem_for(chunk), s>>>(m, L, chunk, uz, uc, low, state, rows,
-                                                                                          ent_seq, static_cast<AT*>(out))));
+  const unsigned blocks = (m.inner + CH - 1) / CH;
+  if (!segments) {
+    const dim3 grid(blocks, rows.n_entries);
+    KLLM_SEQ_DISPATCH(dtype, (ssm_scan_kernel<AT, false><<<grid, kScanThreads, smem_for(chunk), s>>>(
+                                 m, L, chunk, uz, uc, low, state, rows, ent_seq, static_cast<AT*>(out), ScanScratch{})));
+    return done();
+  }
+  const size_t segs = static_cast<size_t>(T) / kScanSeg + rows.n_entries + 1;
+  ScanScratch sc;
+  sc.yl = scratch;
+  sc.cum = sc.yl + static_cast<size_t>(T) * m.inner;
+  sc.send = sc.cum + static_cast<size_t>(T) * m.inner;
+  sc.cend = sc.send + segs * m.inner * m.state;
+  const dim3 grid(blocks, (max_count + kScanSeg - 1) / kScanSeg, rows.n_entries);
+  KLLM_SEQ_DISPATCH(dtype, (ssm_scan_kernel<AT, true><<<grid, kScanThreads, smem_for(chunk), s>>>(
+                               m, L, chunk, uz, uc, low, state, rows, ent_seq, static_cast<AT*>(out), sc)));
+  count_launch();
+  const dim3 cgrid((m.inner * m.state + 127) / 128, rows.n_entries);
+  ssm_carry_kernel<<<cgrid, 128, 0, s>>>(m, state, rows, ent_seq, sc);
+  count_launch();
+  KLLM_SEQ_DISPATCH(dtype, (ssm_finish_kernel<AT><<<grid, kScanThreads, 0, s>>>(m, L, uz, low, rows, static_cast<AT*>(out), sc)));
   return done();
 }
 
@@ -553,10 +694,10 @@ int launch_delta_low(int dtype, const kllm_seq_delta& m, const float* proj, void
 
 int launch_delta_prepare(const kllm_seq_delta& m, const float* proj, const float* low2, float* conv_state, const StepRows& rows,
                          float* prep, int T, cudaStream_t s) {
-  const int C = 2 * m.kv_heads * m.dim + m.heads * m.vdim;
-  const size_t smem = static_cast<size_t>(C) * sizeof(float);
+  const size_t smem = (2 * static_cast<size_t>(m.dim) + m.vdim) * sizeof(float);
   if (smem > 48 * 1024) return KLLM_E_UNSUPPORTED;
-  delta_prepare_kernel<<<T, 256, smem, s>>>(m, proj, low2, conv_state, rows, prep);
+  const dim3 grid(T, m.heads);
+  delta_prepare_kernel<<<grid, 128, smem, s>>>(m, proj, low2, conv_state, rows, prep);
   return done();
 }
 

@@ -257,7 +257,8 @@ def test_far_tokens_stay_in_the_recurrent_state(tmp_path, mixer):
     t2[0] = special + 1
     assert rel_err(ref_logits(cfg, w, t2)[-1:], ref[-1:]) > 1e-2  # the construction works
     d = vo.write_model(tmp_path, cfg, w)
-    steps = [whole("a", t[:200], end=False), whole("a", t[200:300], end=False)] + single("a", t[300:])
+    # the second portion is long enough to be cut into segments that are scanned side by side, from a state that is not empty
+    steps = [whole("a", t[:10], end=False), whole("a", t[10:300], end=False)] + single("a", t[300:])
     logits, _ = run_trace(d, steps)
     assert_rows(np.concatenate(logits), ref)
 
