@@ -585,6 +585,9 @@ extern "C" int kllm_seq_step(kllm_seq_engine* e, int32_t n_entries, const int32_
   for (const kllm_seq_layer& L : e->layers)  // and so do the segments of the selective scan
     if (L.mixer_kind == KLLM_SEQ_MIXER_SSM || L.mixer2_kind == KLLM_SEQ_MIXER_SSM)
       ws_bytes = std::max(ws_bytes, ssm_scan_scratch_bytes(L.ssm, T, n_entries, max_count));
+  for (const kllm_seq_layer& L : e->layers)
+    if (L.mixer_kind == KLLM_SEQ_MIXER_DELTA || L.mixer2_kind == KLLM_SEQ_MIXER_DELTA)
+      ws_bytes = std::max(ws_bytes, delta_rule_scratch_bytes(L.delta, T, n_entries, max_count));
   RC(e->ws.reserve(ws_bytes));
   const bool grouped = T >= kGroupedMinTokens;
   if (e->max_top > 0) {
@@ -770,7 +773,7 @@ extern "C" int kllm_seq_step(kllm_seq_engine* e, int32_t n_entries, const int32_
       RC(gemm(dtype, e->q.p, A.w_low2, low2, T, A.decay_rank + A.gate_rank, A.heads * (A.dim + A.vdim), st));
       RC(launch_delta_prepare(A, proj, low2, e->delta_conv[r], step_rows, prep, T, st));
       e->mark(KLLM_SEQ_PHASE_QK_PREPARE);
-      RC(launch_delta_rule(A, prep, e->delta_state[r], step_rows, d_eseq, max_count, o, st));
+      RC(launch_delta_rule(A, prep, e->delta_state[r], step_rows, d_eseq, max_count, T, static_cast<float*>(e->ws.p), o, st));
       RC(launch_delta_out(dtype, A, o, prep, d.norm_eps, e->att.p, T, st));
       e->mark(KLLM_SEQ_PHASE_ATTENTION);
       RC(gemm(dtype, e->att.p, A.w_out, yout, T, A.heads * A.vdim, W, st));

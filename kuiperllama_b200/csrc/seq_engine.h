@@ -289,8 +289,10 @@ int launch_delta_low(int dtype, const kllm_seq_delta& m, const float* proj, void
 int launch_delta_prepare(const kllm_seq_delta& m, const float* proj, const float* low2, float* conv_state, const StepRows& rows,
                          float* prep, int T, cudaStream_t s);
 // the recurrence of every entry from its sequence's state ([slots][heads][dim][vdim] fp32); o [T, heads*vdim] fp32
+// Steps with long entries walk segments of an entry in parallel through `scratch` (delta_rule_scratch_bytes(); 0: not needed).
+size_t delta_rule_scratch_bytes(const kllm_seq_delta& m, int T, int n_entries, int max_count);
 int launch_delta_rule(const kllm_seq_delta& m, const float* prep, float* state, const StepRows& rows, const int32_t* ent_seq,
-                      int max_count, float* o, cudaStream_t s);
+                      int max_count, int T, float* scratch, float* o, cudaStream_t s);
 // out[t, h] = o[t, h] / rms(o[t, h]) * norm_w * gate[t, h] in the compute type
 int launch_delta_out(int dtype, const kllm_seq_delta& m, const float* o, const float* prep, float eps, void* out, int T,
                      cudaStream_t s);

@@ -457,31 +457,52 @@ __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wai
 // Chunks of `chunk` rows (q, k, g of the head, v of the CTA's columns, beta) come through two shared-memory buffers by
 // cp.async: the next chunk is on its way while the current one is worked on.  VEC: every part of a prepared row starts on
 // 16 bytes (dim and vdim multiples of 4), so the copies are 16 bytes wide.
-template <int RP, bool VEC>
+// Only the prediction's dot product is joined over the lanes inside the loop over rows (the next row's state waits for
+// it); the read-out leaves its per-lane parts in shared memory and they are added when the chunk is written out.
+//
+// Long entries (MODE 1 and 2; MODE 0 walks a whole entry).  A row maps the state linearly, S_t = M_t S_(t-1) + k_t u'_t with
+// M_t = (I - beta k k^T) diag(g), so an entry is cut into segments of kDeltaSeg rows that are walked at the same time:
+//   MODE 1   every segment from an empty state (the first from the sequence's), with dim more columns that start as the
+//            identity and are fed zero values: they end as the segment's product of the M_t.  No read-out.  The end states
+//            go to the scratch E [segment][head][dim][vdim + dim].
+//   carry    the start state of every segment, one after the other: S_start(s+1) = S'_end(s) + M(s) S_start(s); it
+//            replaces S'_end(s) in E; the last one is the sequence's new state
+//   MODE 2   every segment again, from its start state, with the read-out (the first segment starts from the copy of the
+//            sequence's old state that MODE 1 left behind the blocks of E: the carry has overwritten the state by then)
+constexpr int kDeltaSeg = 128;
+constexpr int kDeltaParallelFrom = 256;
+__host__ __device__ inline int delta_segment_id(int first, int e, int seg) { return first / kDeltaSeg + e + seg; }
+
+template <int RP, int L, bool VEC, int MODE>
 __global__ void __launch_bounds__(kDeltaThreads)
-delta_rule_kernel(kllm_seq_delta m, int L, int chunk, const float* __restrict__ prep, float* __restrict__ state,
-                  StepRows rows, const int32_t* __restrict__ ent_seq, float* __restrict__ o) {
-  const int e = blockIdx.z, h = blockIdx.y;
-  const int first = rows.ent_first[e], count = rows.ent_count[e], pos0 = rows.ent_pos0[e], seq = ent_seq[e];
-  const int COLS = kDeltaThreads / L;
+delta_rule_kernel(kllm_seq_delta m, int chunk, const float* __restrict__ prep, float* __restrict__ state,
+                  StepRows rows, const int32_t* __restrict__ ent_seq, float* __restrict__ o, float* __restrict__ E,
+                  float* __restrict__ S0, int segs_max) {
+  const int e = MODE ? blockIdx.z / segs_max : blockIdx.z, seg = MODE ? blockIdx.z % segs_max : 0, h = blockIdx.y;
+  const int e_first = rows.ent_first[e], e_count = rows.ent_count[e], pos0 = rows.ent_pos0[e], seq = ent_seq[e];
+  if (MODE && seg * kDeltaSeg >= e_count) return;
+  const int first = MODE ? e_first + seg * kDeltaSeg : e_first;
+  const int count = MODE ? min(kDeltaSeg, e_count - seg * kDeltaSeg) : e_count;
+  constexpr int COLS = kDeltaThreads / L;
   const int lane = threadIdx.x % L, jl = threadIdx.x / L, j0 = blockIdx.x * COLS, j = j0 + jl;
-  const bool live = j < m.vdim;
+  const int ncols = MODE == 1 ? m.vdim + m.dim : m.vdim;  // MODE 1: the identity columns follow the value columns
+  const bool live = j < ncols, ident = MODE == 1 && j >= m.vdim;
   const int D = m.dim, vn = m.heads * m.vdim;
   const int g = h / (m.heads / m.kv_heads);
   const int prow = delta_prep_row(m);
   const DeltaRow at = delta_row(m);
   const int off_q = at.q + g * D, off_k = at.k + g * D, off_v = at.v + h * m.vdim + j0, off_g = at.decay + h * D,
             off_b = at.beta + h;
-  const int LS = RP + kDeltaPad, DP = L * LS;      // a lane's slice, a row of q / k / g in shared memory
-  const int per = 3 * DP + COLS + 4;               // floats of one row of a chunk: q | k | g | v | beta (+ pad)
+  constexpr int LS = RP + kDeltaPad, DP = L * LS;  // a lane's slice, a row of q / k / g in shared memory
+  constexpr int per = 3 * DP + COLS + 4;           // floats of one row of a chunk: q | k | g | v | beta (+ pad)
   extern __shared__ __align__(16) float sm[];
-  float* o_s = sm + 2 * chunk * per;               // [chunk][COLS]
+  float* o_s = sm + 2 * chunk * per;               // [chunk][COLS][L] the read-out's parts
   for (int i = threadIdx.x; i < 2 * chunk * per; i += kDeltaThreads) sm[i] = 0.f;  // the padding stays zero
   __syncthreads();
 
   auto stage = [&](int r0, int nr, float* buf) {
     if (VEC) {
-      const int dv = D / 4, cv = min(COLS, m.vdim - j0) / 4;
+      const int dv = D / 4, cv = max(0, min(COLS, m.vdim - j0)) / 4;
       const int tasks = nr * (3 * dv + cv);
       for (int i = threadIdx.x; i < tasks; i += kDeltaThreads) {
         const int r = i / (3 * dv + cv), x = i % (3 * dv + cv);
@@ -495,7 +516,7 @@ delta_rule_kernel(kllm_seq_delta m, int L, int chunk, const float* __restrict__ 
         }
       }
     } else {
-      const int cv = min(COLS, m.vdim - j0);
+      const int cv = max(0, min(COLS, m.vdim - j0));
       const int tasks = nr * (3 * D + cv);
       for (int i = threadIdx.x; i < tasks; i += kDeltaThreads) {
         const int r = i / (3 * D + cv), x = i % (3 * D + cv);
@@ -515,11 +536,20 @@ delta_rule_kernel(kllm_seq_delta m, int L, int chunk, const float* __restrict__ 
   };
 
   float S[RP];
-  float* st = state + ((static_cast<size_t>(seq) * m.heads + h) * D) * m.vdim + (live ? j : 0);
+  float* st = state + ((static_cast<size_t>(seq) * m.heads + h) * D) * m.vdim + (live && !ident ? j : 0);
+  // this segment's block of E: [dim][vdim + dim]
+  float* Es = MODE ? E + ((static_cast<size_t>(delta_segment_id(e_first, e, seg)) * m.heads + h) * D) * (m.vdim + D) + (live ? j : 0)
+                   : nullptr;
 #pragma unroll
   for (int x = 0; x < RP; ++x) {
     const int i = lane * RP + x;
-    S[x] = live && i < D && pos0 > 0 ? st[static_cast<size_t>(i) * m.vdim] : 0.f;
+    const bool on = live && i < D;
+    // the copy of the entry's old state: [entry][head][dim][vdim]
+    float* keep = MODE ? S0 + ((static_cast<size_t>(e) * m.heads + h) * D + i) * m.vdim + j : nullptr;
+    if (ident) S[x] = on && i == j - m.vdim ? 1.0f : 0.f;
+    else if (MODE == 2) S[x] = on ? (seg > 0 ? Es[static_cast<size_t>(i) * (m.vdim + D)] : *keep) : 0.f;
+    else S[x] = on && pos0 > 0 && seg == 0 ? st[static_cast<size_t>(i) * m.vdim] : 0.f;
+    if (MODE == 1 && seg == 0 && on && !ident) *keep = S[x];
   }
   stage(0, min(chunk, count), sm);
   int which = 0;
@@ -543,6 +573,7 @@ delta_rule_kernel(kllm_seq_delta m, int L, int chunk, const float* __restrict__ 
         p2 = fmaf(S[4 * x + 2], kk.z, p2), p3 = fmaf(S[4 * x + 3], kk.w, p3);
       }
       float pred = (p0 + p1) + (p2 + p3);
+#pragma unroll
       for (int w = L >> 1; w > 0; w >>= 1) pred += __shfl_xor_sync(kAll, pred, w);
       const float u = row[3 * DP + COLS] * (row[3 * DP + jl] - pred);
       p0 = p1 = p2 = p3 = 0.f;
@@ -554,20 +585,93 @@ delta_rule_kernel(kllm_seq_delta m, int L, int chunk, const float* __restrict__ 
         p0 = fmaf(S[4 * x], qq.x, p0), p1 = fmaf(S[4 * x + 1], qq.y, p1);
         p2 = fmaf(S[4 * x + 2], qq.z, p2), p3 = fmaf(S[4 * x + 3], qq.w, p3);
       }
-      float out = (p0 + p1) + (p2 + p3);
-      for (int w = L >> 1; w > 0; w >>= 1) out += __shfl_xor_sync(kAll, out, w);
-      if (lane == 0) o_s[r * COLS + jl] = out;
+      if (MODE != 1) o_s[r * kDeltaThreads + threadIdx.x] = (p0 + p1) + (p2 + p3);
     }
     __syncthreads();
-    for (int i = threadIdx.x; i < nr * COLS; i += kDeltaThreads) {
+    for (int i = threadIdx.x; MODE != 1 && i < nr * COLS; i += kDeltaThreads) {
       const int jj = j0 + i % COLS;
-      if (jj < m.vdim) o[static_cast<size_t>(first + r0 + i / COLS) * vn + h * m.vdim + jj] = o_s[i];
+      float out = 0.f;
+#pragma unroll
+      for (int l = 0; l < L; ++l) out += o_s[i * L + l];
+      if (jj < m.vdim) o[static_cast<size_t>(first + r0 + i / COLS) * vn + h * m.vdim + jj] = out;
     }
   }
+  if (MODE == 2) return;  // the carry wrote the sequence's new state
 #pragma unroll
   for (int x = 0; x < RP; ++x) {
     const int i = lane * RP + x;
-    if (live && i < D) st[static_cast<size_t>(i) * m.vdim] = S[x];
+    if (live && i < D) {
+      if (MODE == 1) Es[static_cast<size_t>(i) * (m.vdim + D)] = S[x];
+      else st[static_cast<size_t>(i) * m.vdim] = S[x];
+    }
+  }
+}
+
+// One CTA: one entry, one head, JB = groups * kCarryCols value columns; thread (i, group) owns S[i][its kCarryCols
+// columns].  Per segment the product M(s) S_start(s) goes through shared memory: M in tiles of 32 columns (read along its
+// rows, so the loads are coalesced), S_start(s) as the CTA's columns of the state at hand.
+constexpr int kCarryCols = 8;
+constexpr int kCarryTile = 32;
+__global__ void __launch_bounds__(256)
+delta_carry_kernel(kllm_seq_delta m, float* __restrict__ state, StepRows rows, const int32_t* __restrict__ ent_seq,
+                   float* __restrict__ E, int groups) {
+  extern __shared__ float sm[];
+  const int e = blockIdx.z, h = blockIdx.y;
+  const int first = rows.ent_first[e], count = rows.ent_count[e];
+  const int D = m.dim, V = m.vdim, EW = V + D, JB = groups * kCarryCols;
+  float* Ms = sm;                          // [D][kCarryTile + 1]
+  float* cur = Ms + D * (kCarryTile + 1);  // [D][JB]
+  const int i = threadIdx.x % D, grp = threadIdx.x / D;
+  const bool mine = static_cast<int>(threadIdx.x) < groups * D;
+  const int jc = grp * kCarryCols, j0 = blockIdx.x * JB + jc;  // this thread's columns: j0 .. j0 + kCarryCols - 1
+  const int segs = (count + kDeltaSeg - 1) / kDeltaSeg;
+  auto block = [&](int sgm) { return E + ((static_cast<size_t>(delta_segment_id(first, e, sgm)) * m.heads + h) * D) * EW; };
+  float c[kCarryCols];
+  {
+    const float* E0 = block(0) + static_cast<size_t>(i) * EW;  // the first segment started from the sequence's state
+#pragma unroll
+    for (int x = 0; x < kCarryCols; ++x) c[x] = mine && j0 + x < V ? E0[j0 + x] : 0.f;
+  }
+  for (int sgm = 1; sgm < segs; ++sgm) {
+    float* Es = block(sgm);
+    __syncthreads();  // the previous segment's reads of cur and Ms are over
+    if (mine) {
+#pragma unroll
+      for (int x = 0; x < kCarryCols; ++x) cur[i * JB + jc + x] = c[x];
+    }
+    float acc[kCarryCols];
+#pragma unroll
+    for (int x = 0; x < kCarryCols; ++x) acc[x] = mine && j0 + x < V ? Es[static_cast<size_t>(i) * EW + j0 + x] : 0.f;
+    for (int l0 = 0; l0 < D; l0 += kCarryTile) {
+      __syncthreads();  // cur is written; the previous tile is no longer read
+      for (int idx = threadIdx.x; idx < D * kCarryTile; idx += blockDim.x) {
+        const int r = idx / kCarryTile, l = idx % kCarryTile;
+        Ms[r * (kCarryTile + 1) + l] = l0 + l < D ? Es[static_cast<size_t>(r) * EW + V + l0 + l] : 0.f;
+      }
+      __syncthreads();
+      if (mine) {
+        const int nl = min(kCarryTile, D - l0);
+        for (int l = 0; l < nl; ++l) {
+          const float mv = Ms[i * (kCarryTile + 1) + l];
+          const float* cr = cur + (l0 + l) * JB + jc;
+#pragma unroll
+          for (int x = 0; x < kCarryCols; ++x) acc[x] = fmaf(mv, cr[x], acc[x]);
+        }
+      }
+    }
+    if (mine) {
+#pragma unroll
+      for (int x = 0; x < kCarryCols; ++x) {
+        if (j0 + x < V) Es[static_cast<size_t>(i) * EW + j0 + x] = c[x];  // the segment's start state, for the second pass
+        c[x] = acc[x];
+      }
+    }
+  }
+  if (mine) {
+    float* out = state + ((static_cast<size_t>(ent_seq[e]) * m.heads + h) * D + i) * V;
+#pragma unroll
+    for (int x = 0; x < kCarryCols; ++x)
+      if (j0 + x < V) out[j0 + x] = c[x];
   }
 }
 
@@ -701,29 +805,63 @@ int launch_delta_prepare(const kllm_seq_delta& m, const float* proj, const float
   return done();
 }
 
+size_t delta_rule_scratch_bytes(const kllm_seq_delta& m, int T, int n_entries, int max_count) {
+  if (max_count <= kDeltaParallelFrom) return 0;
+  const size_t segs = static_cast<size_t>(T) / kDeltaSeg + n_entries + 1;
+  return (segs * m.heads * m.dim * (m.vdim + m.dim) + static_cast<size_t>(n_entries) * m.heads * m.dim * m.vdim) * sizeof(float);
+}
+
 int launch_delta_rule(const kllm_seq_delta& m, const float* prep, float* state, const StepRows& rows, const int32_t* ent_seq,
-                      int max_count, float* o, cudaStream_t s) {
+                      int max_count, int T, float* scratch, float* o, cudaStream_t s) {
   // 16 rows of a column per thread while that leaves at most 8 lanes to a column, else 32
   const int RP = m.dim <= 128 ? 16 : 32;
-  if (m.dim > 32 * RP || m.dim > 256) return KLLM_E_UNSUPPORTED;
+  if (m.dim > 256) return KLLM_E_UNSUPPORTED;
   const int L = lanes_for(m.dim, RP);
   const int COLS = kDeltaThreads / L;
   const int per = 3 * L * (RP + kDeltaPad) + COLS + 4;
-  auto smem_for = [&](int chunk) { return (2 * static_cast<size_t>(chunk) * per + static_cast<size_t>(chunk) * COLS) * sizeof(float); };
+  const bool segments = max_count > kDeltaParallelFrom && scratch != nullptr;
+  const int longest = segments ? kDeltaSeg : max_count;
+  auto smem_for = [&](int chunk) { return (2 * static_cast<size_t>(chunk) * per + static_cast<size_t>(chunk) * kDeltaThreads) * sizeof(float); };
   int chunk = 16;
-  while (chunk > 1 && (smem_for(chunk) > 48 * 1024 || chunk / 2 >= max_count)) chunk /= 2;
+  while (chunk > 1 && (smem_for(chunk) > 48 * 1024 || chunk / 2 >= longest)) chunk /= 2;
   if (smem_for(chunk) > 48 * 1024) return KLLM_E_UNSUPPORTED;
   const bool vec = m.dim % 4 == 0 && m.vdim % 4 == 0;
-  const dim3 grid((m.vdim + COLS - 1) / COLS, m.heads, rows.n_entries);
-#define KLLM_DELTA(R, V) delta_rule_kernel<R, V><<<grid, kDeltaThreads, smem_for(chunk), s>>>(m, L, chunk, prep, state, rows, ent_seq, o)
-  if (RP == 16) {
-    if (vec) KLLM_DELTA(16, true);
-    else KLLM_DELTA(16, false);
-  } else {
-    if (vec) KLLM_DELTA(32, true);
-    else KLLM_DELTA(32, false);
+  const int segs_max = segments ? (max_count + kDeltaSeg - 1) / kDeltaSeg : 1;
+  float* keep = segments ? scratch + (static_cast<size_t>(T) / kDeltaSeg + rows.n_entries + 1) * m.heads * m.dim * (m.vdim + m.dim)
+                         : nullptr;
+#define KLLM_DELTA_M(R, LN, MODE, COLSN)                                                                                  \
+  do {                                                                                                                    \
+    const dim3 grid(((COLSN) + COLS - 1) / COLS, m.heads, rows.n_entries * segs_max);                                      \
+    if (vec)                                                                                                              \
+      delta_rule_kernel<R, LN, true, MODE><<<grid, kDeltaThreads, smem_for(chunk), s>>>(m, chunk, prep, state, rows, ent_seq, o, \
+                                                                                         scratch, keep, segs_max);       \
+    else                                                                                                                  \
+      delta_rule_kernel<R, LN, false, MODE><<<grid, kDeltaThreads, smem_for(chunk), s>>>(m, chunk, prep, state, rows, ent_seq, o, \
+                                                                                          scratch, keep, segs_max);      \
+  } while (0)
+#define KLLM_DELTA(MODE, COLSN)                      \
+  do {                                               \
+    if (RP == 32) KLLM_DELTA_M(32, 8, MODE, COLSN);  \
+    else if (L == 1) KLLM_DELTA_M(16, 1, MODE, COLSN); \
+    else if (L == 2) KLLM_DELTA_M(16, 2, MODE, COLSN); \
+    else if (L == 4) KLLM_DELTA_M(16, 4, MODE, COLSN); \
+    else KLLM_DELTA_M(16, 8, MODE, COLSN);           \
+  } while (0)
+  if (!segments) {
+    KLLM_DELTA(0, m.vdim);
+    return done();
   }
+  KLLM_DELTA(1, m.vdim + m.dim);
+  count_launch();
+  const int groups = std::max(1, std::min(8, 256 / m.dim));
+  const int JB = groups * kCarryCols;
+  const dim3 cgrid((m.vdim + JB - 1) / JB, m.heads, rows.n_entries);
+  const size_t csmem = (static_cast<size_t>(m.dim) * (kCarryTile + 1) + static_cast<size_t>(m.dim) * JB) * sizeof(float);
+  delta_carry_kernel<<<cgrid, 256, csmem, s>>>(m, state, rows, ent_seq, scratch, groups);
+  count_launch();
+  KLLM_DELTA(2, m.vdim);
 #undef KLLM_DELTA
+#undef KLLM_DELTA_M
   return done();
 }
 

@@ -263,6 +263,25 @@ def test_far_tokens_stay_in_the_recurrent_state(tmp_path, mixer):
     assert_rows(np.concatenate(logits), ref)
 
 
+def test_long_entries_are_walked_in_segments(tmp_path):
+    """Entries of several hundred rows: the recurrences cut them into segments that run side by side and are joined by a
+    carry -- from an empty state, from a state that earlier rows left, beside a short entry, and with decoding afterwards."""
+    layers = [(vo.mamba_mixer(inner=24, state=6, dt_rank=3, conv=4), None),
+              (par(left=dict(window=30), right=dict(heads=4, kv_heads=2, dim=12, vdim=8, conv=3)), vo.dense_mlp(24))]
+    cfg = vo.make_config(width=32, vocab=40, layers=layers, loop=(0, 2, 2))
+    w = vo.make_weights(cfg, seed=91)
+    d = vo.write_model(tmp_path, cfg, w)
+    a, b = toks(5 + 600 + 3, cfg["vocab"], 92), toks(390 + 7, cfg["vocab"], 93)
+    steps = [{"entries": [{"id": "a", "tokens": a[:5], "want": [4]}]},
+             {"entries": [{"id": "a", "tokens": a[5:605], "want": list(range(600))},
+                          {"id": "b", "tokens": b[:7], "want": list(range(7))}]},
+             {"entries": [{"id": "b", "tokens": b[7:], "want": list(range(390))}]}] + single("a", a[605:])
+    logits, _ = run_trace(d, steps, max_tokens=1100)
+    ra, rb = ref_logits(cfg, w, a), ref_logits(cfg, w, b)
+    assert_rows(np.concatenate([logits[0], logits[1][:600]] + logits[3:]), ra[4:])
+    assert_rows(np.concatenate([logits[1][600:], logits[2]]), rb)
+
+
 # ---- prompt against token-by-token decoding, long decoding ----------------------------------------------------------
 def test_prefill_equals_stepwise_decoding(base):
     cfg, w, d = base
