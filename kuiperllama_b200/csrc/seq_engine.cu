@@ -8,7 +8,8 @@
 // returns them at close.  The table rows of the step's sequences are copied to the device before the kernels run.
 //
 // State.  Beside the pages, every layer run owns per-slot recurrent state in fp32: the last mixer input of a layer with a
-// token shift, and the matrix state of linear attention.  A sequence of length 0 reads zeros instead of its slot's
+// token shift, the matrix state of linear attention and of the delta rule, the diagonal state of the selective scan, and
+// the last taps - 1 inputs of every short convolution.  A sequence of length 0 reads zeros instead of its slot's
 // memory, so slots are reused without clearing.  A run of attention through a latent keeps one row per token in its pool
 // (latent | rotated key part); its values are the head of that row.
 //
@@ -25,9 +26,20 @@
 //                              latents (two products) and the tensor-core attention
 //                  linear:     gemm (q | k | v | gate rows), the decayed-state recurrence (one kernel for short entries,
 //                              chunk sums / scan / chunk outputs for long ones), output norm and gate
+//                  attention behind a filter (values = keys): gemm (q | k rows), qk_conv_prepare (bias, short convolution,
+//                              keys as they are into the value pages, rotation, queries / keys out), attention with window,
+//                              kept first tokens, capped scores and sink
+//                  scan:       gemm (u | z rows), ssm_conv (filter + SiLU), gemm (low-rank step | B | C), ssm_scan (one kernel,
+//                              or scan / carry / finish over segments of long entries)
+//                  delta rule: gemm (q | k | v | beta | low-rank rows), delta_low + gemm (second low-rank products),
+//                              delta_prepare (filters, unit vectors, decays, gates), delta_rule (one kernel, or two passes
+//                              over segments with a carry between them), delta_out (per-head norm and gate)
+//                  a layer may run two mixers of different kinds on the same rows; their outputs join x with a weight each
 //     gemm         output projection
 //     resid_norm   x += N_post(y);  h = N_pre_ff(x);  router on h (softmax or sigmoid with groups): same kernel, the row
 //                  is still in shared memory
+//                  (a layer whose feed-forward reads the mixer's input skips this: the first norm kernel routes its row, the
+//                  feed-forward runs on the same rows after the mixers, and ONE sum joins x at the end of the run)
 //     feed-forward dense: gemm, activation, gemm
 //                  experts, few tokens: pair kernels (weights streamed once per chosen expert; a shared expert rides
 //                  along as one more pair per token); many tokens: pairs sorted by expert, two grouped products (SiLU-gate

@@ -644,9 +644,21 @@ delta_carry_kernel(kllm_seq_delta m, float* __restrict__ state, StepRows rows, c
     for (int x = 0; x < kCarryCols; ++x) acc[x] = mine && j0 + x < V ? Es[static_cast<size_t>(i) * EW + j0 + x] : 0.f;
     for (int l0 = 0; l0 < D; l0 += kCarryTile) {
       __syncthreads();  // cur is written; the previous tile is no longer read
-      for (int idx = threadIdx.x; idx < D * kCarryTile; idx += blockDim.x) {
-        const int r = idx / kCarryTile, l = idx % kCarryTile;
-        Ms[r * (kCarryTile + 1) + l] = l0 + l < D ? Es[static_cast<size_t>(r) * EW + V + l0 + l] : 0.f;
+      // eight loads in flight per thread before the first is stored (E is written by this kernel too, so the compiler
+      // keeps loads and stores in program order)
+      constexpr int U = 8;
+      for (int base = threadIdx.x; base < D * kCarryTile; base += blockDim.x * U) {
+        float v[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const int idx = base + u * blockDim.x, r = idx / kCarryTile, l = idx % kCarryTile;
+          v[u] = idx < D * kCarryTile && l0 + l < D ? Es[static_cast<size_t>(r) * EW + V + l0 + l] : 0.f;
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const int idx = base + u * blockDim.x;
+          if (idx < D * kCarryTile) Ms[(idx / kCarryTile) * (kCarryTile + 1) + idx % kCarryTile] = v[u];
+        }
       }
       __syncthreads();
       if (mine) {
