@@ -608,10 +608,11 @@ delta_rule_kernel(kllm_seq_delta m, int chunk, const float* __restrict__ prep, f
 }
 
 // One CTA: one entry, one head, JB = groups * kCarryCols value columns; thread (i, group) owns S[i][its kCarryCols
-// columns].  Per segment the product M(s) S_start(s) goes through shared memory: M in tiles of 32 columns (read along its
-// rows, so the loads are coalesced), S_start(s) as the CTA's columns of the state at hand.
+// columns].  Per segment the product M(s) S_start(s) goes through shared memory: S_start(s) as the CTA's columns of the
+// state at hand, M in tiles of kCarryTile columns.  The tiles of ALL segments are known before the carry starts, so they
+// stream through two buffers by cp.async, one (segment, tile) ahead of the arithmetic; only the state is sequential.
 constexpr int kCarryCols = 8;
-constexpr int kCarryTile = 32;
+constexpr int kCarryTile = 16;
 __global__ void __launch_bounds__(256)
 delta_carry_kernel(kllm_seq_delta m, float* __restrict__ state, StepRows rows, const int32_t* __restrict__ ent_seq,
                    float* __restrict__ E, int groups) {
@@ -619,63 +620,62 @@ delta_carry_kernel(kllm_seq_delta m, float* __restrict__ state, StepRows rows, c
   const int e = blockIdx.z, h = blockIdx.y;
   const int first = rows.ent_first[e], count = rows.ent_count[e];
   const int D = m.dim, V = m.vdim, EW = V + D, JB = groups * kCarryCols;
-  float* Ms = sm;                          // [D][kCarryTile + 1]
-  float* cur = Ms + D * (kCarryTile + 1);  // [D][JB]
+  constexpr int TW = kCarryTile + 1;
+  float* Ms = sm;                 // [2][D][kCarryTile + 1]
+  float* cur = Ms + 2 * D * TW;   // [D][JB]
   const int i = threadIdx.x % D, grp = threadIdx.x / D;
   const bool mine = static_cast<int>(threadIdx.x) < groups * D;
   const int jc = grp * kCarryCols, j0 = blockIdx.x * JB + jc;  // this thread's columns: j0 .. j0 + kCarryCols - 1
-  const int segs = (count + kDeltaSeg - 1) / kDeltaSeg;
+  const int segs = (count + kDeltaSeg - 1) / kDeltaSeg, tiles = (D + kCarryTile - 1) / kCarryTile;
   auto block = [&](int sgm) { return E + ((static_cast<size_t>(delta_segment_id(first, e, sgm)) * m.heads + h) * D) * EW; };
-  float c[kCarryCols];
+  auto fetch = [&](int step) {  // tile step % tiles of segment 1 + step / tiles
+    const float* Es = block(1 + step / tiles);
+    const int l0 = (step % tiles) * kCarryTile;
+    float* dst = Ms + (step & 1) * D * TW;
+    for (int idx = threadIdx.x; idx < D * kCarryTile; idx += blockDim.x) {
+      const int r = idx / kCarryTile, l = idx % kCarryTile;
+      if (l0 + l < D) cp_async4(dst + r * TW + l, Es + static_cast<size_t>(r) * EW + V + l0 + l);
+    }
+    cp_async_commit();
+  };
+  float c[kCarryCols], own[kCarryCols], acc[kCarryCols];
   {
     const float* E0 = block(0) + static_cast<size_t>(i) * EW;  // the first segment started from the sequence's state
 #pragma unroll
     for (int x = 0; x < kCarryCols; ++x) c[x] = mine && j0 + x < V ? E0[j0 + x] : 0.f;
   }
-  for (int sgm = 1; sgm < segs; ++sgm) {
+  const int total = (segs - 1) * tiles;
+  if (total > 0) fetch(0);
+  for (int step = 0; step < total; ++step) {
+    const int sgm = 1 + step / tiles, tile = step % tiles;
     float* Es = block(sgm);
-    __syncthreads();  // the previous segment's reads of cur and Ms are over
-    if (mine) {
+    if (tile == 0) {  // a segment begins: its start state goes to shared memory, its own end state is on its way
+      __syncthreads();  // the previous segment's reads of cur are over
 #pragma unroll
-      for (int x = 0; x < kCarryCols; ++x) cur[i * JB + jc + x] = c[x];
-    }
-    float acc[kCarryCols];
-#pragma unroll
-    for (int x = 0; x < kCarryCols; ++x) acc[x] = mine && j0 + x < V ? Es[static_cast<size_t>(i) * EW + j0 + x] : 0.f;
-    for (int l0 = 0; l0 < D; l0 += kCarryTile) {
-      __syncthreads();  // cur is written; the previous tile is no longer read
-      // eight loads in flight per thread before the first is stored (E is written by this kernel too, so the compiler
-      // keeps loads and stores in program order)
-      constexpr int U = 8;
-      for (int base = threadIdx.x; base < D * kCarryTile; base += blockDim.x * U) {
-        float v[U];
-#pragma unroll
-        for (int u = 0; u < U; ++u) {
-          const int idx = base + u * blockDim.x, r = idx / kCarryTile, l = idx % kCarryTile;
-          v[u] = idx < D * kCarryTile && l0 + l < D ? Es[static_cast<size_t>(r) * EW + V + l0 + l] : 0.f;
-        }
-#pragma unroll
-        for (int u = 0; u < U; ++u) {
-          const int idx = base + u * blockDim.x;
-          if (idx < D * kCarryTile) Ms[(idx / kCarryTile) * (kCarryTile + 1) + idx % kCarryTile] = v[u];
-        }
-      }
-      __syncthreads();
-      if (mine) {
-        const int nl = min(kCarryTile, D - l0);
-        for (int l = 0; l < nl; ++l) {
-          const float mv = Ms[i * (kCarryTile + 1) + l];
-          const float* cr = cur + (l0 + l) * JB + jc;
-#pragma unroll
-          for (int x = 0; x < kCarryCols; ++x) acc[x] = fmaf(mv, cr[x], acc[x]);
-        }
+      for (int x = 0; x < kCarryCols; ++x) {
+        if (mine) cur[i * JB + jc + x] = c[x];
+        own[x] = mine && j0 + x < V ? Es[static_cast<size_t>(i) * EW + j0 + x] : 0.f;
+        acc[x] = 0.f;
       }
     }
+    cp_async_wait_all();
+    __syncthreads();  // the tile has landed, cur is written, the other buffer is free
+    if (step + 1 < total) fetch(step + 1);
     if (mine) {
+      const float* mt = Ms + (step & 1) * D * TW + i * TW;
+      const int l0 = tile * kCarryTile, nl = min(kCarryTile, D - l0);
+      for (int l = 0; l < nl; ++l) {
+        const float mv = mt[l];
+        const float* cr = cur + (l0 + l) * JB + jc;
+#pragma unroll
+        for (int x = 0; x < kCarryCols; ++x) acc[x] = fmaf(mv, cr[x], acc[x]);
+      }
+    }
+    if (tile == tiles - 1 && mine) {
 #pragma unroll
       for (int x = 0; x < kCarryCols; ++x) {
         if (j0 + x < V) Es[static_cast<size_t>(i) * EW + j0 + x] = c[x];  // the segment's start state, for the second pass
-        c[x] = acc[x];
+        c[x] = own[x] + acc[x];
       }
     }
   }
@@ -868,7 +868,7 @@ int launch_delta_rule(const kllm_seq_delta& m, const float* prep, float* state, 
   const int groups = std::max(1, std::min(8, 256 / m.dim));
   const int JB = groups * kCarryCols;
   const dim3 cgrid((m.vdim + JB - 1) / JB, m.heads, rows.n_entries);
-  const size_t csmem = (static_cast<size_t>(m.dim) * (kCarryTile + 1) + static_cast<size_t>(m.dim) * JB) * sizeof(float);
+  const size_t csmem = (2 * static_cast<size_t>(m.dim) * (kCarryTile + 1) + static_cast<size_t>(m.dim) * JB) * sizeof(float);
   delta_carry_kernel<<<cgrid, 256, csmem, s>>>(m, state, rows, ent_seq, scratch, groups);
   count_launch();
   KLLM_DELTA(2, m.vdim);
