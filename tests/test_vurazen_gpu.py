@@ -65,6 +65,7 @@ CASES = {
     "scan_no_filter": [(vo.mamba_mixer(inner=16, state=3, dt_rank=2, conv=1), None)],
     "scan_long_filter": [(vo.mamba_mixer(inner=16, state=4, dt_rank=5, conv=7), None)],
     "scan_wide": [(vo.mamba_mixer(inner=200, state=40, dt_rank=9, conv=4), None)],      # more states than a warp has lanes
+    "scan_many_states": [(vo.mamba_mixer(inner=20, state=100, dt_rank=4, conv=3), None)],  # 4 states on each of 32 lanes
     "lightning": [(vo.lightning_mixer(), None)],
     "lightning_one_decay": [(vo.lightning_mixer(heads=2, dim=8, vdim=8, decay=0.9), None)],
     "pair": [(par(), None)],
@@ -85,6 +86,8 @@ CASES = {
     "delta_one_key_head": [(par(right=dict(heads=4, kv_heads=1, dim=5, vdim=9), left_scale=0.0), None)],
     "delta_no_filter": [(par(right=dict(conv=1), left_scale=0.0), None)],
     "delta_wide": [(par(right=dict(heads=2, kv_heads=2, dim=72, vdim=40, conv=4), left_scale=0.0), None)],  # rows of S over 4 lanes
+    "delta_wider": [(par(right=dict(heads=2, kv_heads=1, dim=136, vdim=24, conv=2), left_scale=0.0), None)],  # 32 rows of S per thread
+    "attention_widest": [(par(left=dict(heads=2, kv_heads=2, dim=136, rot_dims=136, window=33, keep_first=1), right_scale=0.0), None)],
     "dense_only": [(vo.lightning_mixer(), vo.dense_mlp(56))],
     "moe_only": [(vo.lightning_mixer(), vo.moe_mlp(6, 2, 16))],
     "moe_no_shared": [(vo.mamba_mixer(), vo.moe_mlp(5, 2, 16, 1.0, None))],
@@ -414,10 +417,11 @@ def test_bfloat16_products(tmp_path):
     assert rel_err(np.concatenate(logits), ref_logits(cfg, w, t)) < TOL16
 
 
-@pytest.mark.parametrize("dim,window,keep", [(24, 17, 0), (64, 64, 3), (128, 150, 70)])
+@pytest.mark.parametrize("dim,window,keep", [(24, 17, 0), (64, 64, 3), (128, 150, 70), (256, 100, 5)])
 def test_bfloat16_prompts_on_the_tensor_cores(tmp_path, dim, window, keep):
     """bf16 prompt steps with head sizes that are multiples of 8 take the tensor-core attention (window, kept first
-    tokens, capped scores, sink): against the float64 restatement, and against single-token steps of the same run."""
+    tokens, capped scores, sink): against the float64 restatement, and against single-token steps of the same run.
+    Heads of 256 are their own values, which is past the tensor-core kernel's value size: they take the split-key kernel."""
     m = par(left=dict(heads=4, kv_heads=2, dim=dim, rot_dims=16, window=window, keep_first=keep, softcap=8.0),
             right_scale=0.0, left_scale=1.0)
     cfg = vo.make_config(width=64, vocab=80, layers=[(m, None)])
