@@ -33,7 +33,7 @@ def build_oracle() -> Path:
 def build_ref(jobs: int = 8) -> bool:
     """Compile oracle/_ref from /root/reference when that tree is present (build container);
     on the GPU box the prebuilt .so files that travelled with the snapshot are used."""
-    if not REFERENCE_TREE.is_dir():
+    if not REFERENCE_TREE.is_dir() or not any(REFERENCE_TREE.iterdir()):  # no tree, or an empty one
         return REF_SO.exists()
     subprocess.check_call(["make", "-s", f"-j{jobs}", "-C", str(HERE), "ref"])
     return True
