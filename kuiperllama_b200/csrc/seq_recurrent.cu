@@ -481,6 +481,9 @@ delta_rule_kernel(kllm_seq_delta m, int chunk, const float* __restrict__ prep, f
   const int e = MODE ? blockIdx.z / segs_max : blockIdx.z, seg = MODE ? blockIdx.z % segs_max : 0, h = blockIdx.y;
   const int e_first = rows.ent_first[e], e_count = rows.ent_count[e], pos0 = rows.ent_pos0[e], seq = ent_seq[e];
   if (MODE && seg * kDeltaSeg >= e_count) return;
+  // the product of an entry's first segment is never used (that segment starts from the sequence's own state): CTAs that
+  // hold identity columns only have nothing to do there.  (The last segment's is: the carry ends with the new state.)
+  if (MODE == 1 && seg == 0 && static_cast<int>(blockIdx.x) * (kDeltaThreads / L) >= m.vdim) return;
   const int first = MODE ? e_first + seg * kDeltaSeg : e_first;
   const int count = MODE ? min(kDeltaSeg, e_count - seg * kDeltaSeg) : e_count;
   constexpr int COLS = kDeltaThreads / L;

@@ -270,7 +270,7 @@ def test_long_entries_are_walked_in_segments(tmp_path):
     """Entries of several hundred rows: the recurrences cut them into segments that run side by side and are joined by a
     carry -- from an empty state, from a state that earlier rows left, beside a short entry, and with decoding afterwards."""
     layers = [(vo.mamba_mixer(inner=24, state=6, dt_rank=3, conv=4), None),
-              (par(left=dict(window=30), right=dict(heads=4, kv_heads=2, dim=12, vdim=8, conv=3)), vo.dense_mlp(24))]
+              (par(left=dict(window=30), right=dict(heads=4, kv_heads=2, dim=40, vdim=24, conv=3)), vo.dense_mlp(24))]
     cfg = vo.make_config(width=32, vocab=40, layers=layers, loop=(0, 2, 2))
     w = vo.make_weights(cfg, seed=91)
     d = vo.write_model(tmp_path, cfg, w)
