@@ -30,12 +30,24 @@ extern "C" {
 #define KLLM_SEQ_MIXER_LINEAR 3    /* linear attention with a decayed matrix state per head (no cache, a recurrent state) */
 #define KLLM_SEQ_MIXER_SSM 4       /* selective scan: short convolution, input-dependent step sizes, a diagonal state per channel */
 #define KLLM_SEQ_MIXER_DELTA 5     /* gated delta rule: a matrix state per head, decayed per key channel and corrected towards each value */
+#define KLLM_SEQ_MIXER_SSD 6       /* state-space duality: short convolution, one input-dependent decay per head, a matrix state per head */
 #define KLLM_SEQ_FF_NONE 0
 #define KLLM_SEQ_FF_MOE 1   /* routed experts (softmax or sigmoid router), optional gated shared expert */
 #define KLLM_SEQ_FF_DENSE 2 /* down(act(up h)) */
 
 #define KLLM_SEQ_NORM_LAYER 0 /* (v - mean) / sqrt(var + eps) * w + b */
 #define KLLM_SEQ_NORM_RMS 1   /* v / sqrt(mean(v^2) + eps) * w */
+#define KLLM_SEQ_NORM_NONE 2  /* v itself (w is not read): a sublayer that reads the residual stream as it is */
+
+/* output gate of an attention (kllm_seq_attention.gate) */
+#define KLLM_SEQ_GATE_NONE 0
+#define KLLM_SEQ_GATE_HEAD 1    /* one sigmoid gate per (token, head): `heads` gate rows close w_in */
+#define KLLM_SEQ_GATE_ELEMENT 2 /* one sigmoid gate per output element: heads * vdim gate rows close w_in */
+
+/* norm of every query / key head (kllm_seq_attention.qk_norm) */
+#define KLLM_SEQ_QKNORM_NONE 0
+#define KLLM_SEQ_QKNORM_WEIGHTED 1 /* RMS norm over dim with q_norm_w / k_norm_w, before the rotation */
+#define KLLM_SEQ_QKNORM_UNIT 2     /* x / sqrt(mean(x^2) + eps) without weights, after the rotation */
 
 /* activations of a feed-forward's inner layer */
 #define KLLM_SEQ_ACT_SWIGLU 0 /* silu(gate h) * (up h): the weights hold gate rows, then up rows */
@@ -62,9 +74,10 @@ typedef struct kllm_seq_attention {
   float scale;                        /* score = (q . k) * scale */
   float temp_coef;                    /* query temperature 1 + coef * ln(floor((pos + 1) / every) + 1) ... */
   int32_t temp_every;                 /* ... 0: none */
-  int32_t qk_norm;                    /* RMS norm over dim of each query / key head, weights below */
-  int32_t gate;                       /* sigmoid output gate per (token, head); its rows close w_in */
-  const void* w_in;  /* [heads*dim + kv_heads*dim + kv_heads*vdim (+ heads), width]: q | k | v (| gate) rows, compute type */
+  int32_t qk_norm;                    /* KLLM_SEQ_QKNORM_*: norm over dim of each query / key head */
+  int32_t gate;                       /* KLLM_SEQ_GATE_*: sigmoid output gate; its rows close w_in */
+  const void* w_in;  /* [heads*dim + kv_heads*dim + kv_heads*vdim (+ gate rows), width]: q | k | v (| gate) rows, compute type
+                        (differential: 2*heads*dim query rows and 2*kv_heads*dim key rows) */
   const float* q_norm_w; /* [dim] */
   const float* k_norm_w; /* [dim] */
   const void* w_out;     /* [width, heads*vdim], compute type */
@@ -81,6 +94,15 @@ typedef struct kllm_seq_attention {
   float rope_base;       /* angle of pair i = position * rope_base^(-2 i / rope_dims) */
   int32_t rope_pairing;  /* KLLM_SEQ_ROPE_* */
   int32_t values_are_keys; /* the values are the keys as they are before the rotation: w_in has no value rows, vdim == dim */
+  const float* rope_freq;  /* [rope_dims / 2] fp32: angle of pair i = position * rope_freq[i] (any frequency scaling is
+                              folded into this table), or NULL: rope_base^(-2 i / rope_dims) */
+  float rope_mag;          /* cos and sin are multiplied by it (the rotated coordinates grow by this factor); 0 means 1 */
+  /* Differential attention (!= 0): every query head and every key head holds TWO maps of `dim` coordinates, laid out
+   * head by head as [map 1 | map 2]; head norms and rotation act on each map; each map is a softmax attention of its
+   * own over the head's values (a1, a2), and the head's output is o = a1 - diff_lambda * a2, then
+   * o / sqrt(mean(o^2) + eps) * diff_out_scale over its vdim values. */
+  int32_t differential;
+  float diff_lambda, diff_out_scale;
 } kllm_seq_attention;
 
 /* Attention through a latent.  Queries: cq = RMSnorm(W_dq h), q = W_uq cq, per head [dim plain | rot_dim rotated].
@@ -146,6 +168,24 @@ typedef struct kllm_seq_delta {
   const void* w_out;       /* [width, heads*vdim] */
 } kllm_seq_delta;
 
+/* State-space duality (a selective scan whose decay is ONE number per head and token).  inner = heads * vdim.
+ * W_in h = [z: inner | x: inner | B: groups*state | C: groups*state | dt: heads]; x, B and C together pass a causal
+ * convolution per channel and SiLU; dt <- softplus(dt + dt_bias) (no clamp).  Head h reads B, C of group h / (heads / groups):
+ * S <- exp(a_h dt) S + dt B x^T (S is state x vdim), y = S^T C + d_h x.  Then y * silu(z), an RMS norm in norm_groups
+ * equal parts of inner (each part by its own root mean square) times out_norm_w, and W_out.  S and the last
+ * conv_taps - 1 inputs of the convolution are fp32 state of the sequence. */
+typedef struct kllm_seq_ssd {
+  int32_t heads, vdim, state, groups, conv_taps, norm_groups;
+  const void* w_in;        /* [2 * inner + 2 * groups * state + heads, width] */
+  const float* conv_w;     /* [inner + 2 * groups * state][conv_taps] fp32, the last column weighs the current token */
+  const float* conv_b;     /* [inner + 2 * groups * state] or NULL */
+  const float* dt_bias;    /* [heads] */
+  const float* a;          /* [heads] fp32: the rates, already negative (-exp(A_log)) */
+  const float* d;          /* [heads] */
+  const float* out_norm_w; /* [inner] */
+  const void* w_out;       /* [width, inner] */
+} kllm_seq_ssd;
+
 typedef struct kllm_seq_dense {
   int32_t ff, act;    /* inner size; KLLM_SEQ_ACT_* (XIELU, RELU2, or RELU_GATE: then `up` holds ff gate rows followed by ff up rows) */
   float act_a, act_b; /* the two coefficients of KLLM_SEQ_ACT_XIELU */
@@ -176,7 +216,8 @@ typedef struct kllm_seq_moe {
 typedef struct kllm_seq_layer {
   int32_t mixer_kind; /* KLLM_SEQ_MIXER_* */
   int32_t ff_kind;    /* KLLM_SEQ_FF_* */
-  /* x += post_mixer(mixer(pre_mixer(x)));  x += post_ff(ff(pre_ff(x))) */
+  /* x += post_mixer(mixer(pre_mixer(x)));  x += post_ff(ff(pre_ff(x)));  a pre-norm of kind KLLM_SEQ_NORM_NONE hands x
+   * itself to the sublayer */
   kllm_seq_norm pre_mixer, post_mixer, pre_ff, post_ff;
   kllm_seq_attention attn;
   kllm_seq_moe moe;
@@ -196,6 +237,9 @@ typedef struct kllm_seq_layer {
   /* != 0: the feed-forward reads the mixer's input too (pre_mixer's output; pre_ff is not used) and
    * x += mixer(...) + ff(...) in one step */
   int32_t parallel_ff;
+  kllm_seq_ssd ssd;
+  /* RMS norms over the model width on each mixer's own output, before the mixers' weighted sum (w == NULL: none) */
+  kllm_seq_norm mixer_out_norm, mixer2_out_norm;
 } kllm_seq_layer;
 
 typedef struct kllm_seq_desc {

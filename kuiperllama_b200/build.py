@@ -88,7 +88,7 @@ SEQ_TOOLS_DIR = KUIPER / "_build" / "seq"
 # family registered with KLLM_REGISTER_SEQUENCE_MODEL
 SEQ_HOST_SOURCES = ["source/base/alloc.cpp", "source/base/buffer.cpp", "source/model/safetensors.cpp",
                     "source/model/sequence_model.cpp", "source/model/fobolorn.cpp",
-                    "source/model/kikunex.cpp", "source/model/vurazen.cpp"]
+                    "source/model/kikunex.cpp", "source/model/vurazen.cpp", "source/model/bukuvik.cpp"]
 SEQ_TOOLS = ["kuiper_trace", "kuiper_generate"]
 CUDA_HOME = Path(os.environ.get("CUDA_HOME", "/usr/local/cuda"))
 

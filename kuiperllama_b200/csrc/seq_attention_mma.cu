@@ -98,6 +98,7 @@ attention_mma_kernel(AttnShape a, const __nv_bfloat16* __restrict__ q, PagedKV k
   // grid: x = (entry, key/value head), y = row tile, z = split.  CTAs are handed out in x-fastest order, so the tiles
   // of equal weight (the same rows of every head) start together, heaviest first
   const int e = blockIdx.x / a.kv_heads, g = blockIdx.x % a.kv_heads, split = blockIdx.z;
+  const int gv = g / v_share_of(a);  // the value head this key head reads
   const int rep = a.heads / a.kv_heads;
   const int dim = a.dim, vdim = a.vdim;  // <= DIM, VDIM; multiples of 8
   const int count = ent_count[e], first = ent_first[e], seq = ent_seq[e], pos0 = ent_pos0[e];
@@ -178,7 +179,7 @@ attention_mma_kernel(AttnShape a, const __nv_bfloat16* __restrict__ q, PagedKV k
       } else {
         const bool in = valid && (c - KC) * 8 < vdim;
         cp_async16(vs_addr + ((stage * kKeys + j) * LDV + (c - KC) * 8) * 2,
-                   in ? vbase + slot * kv.v_row + g * vdim + (c - KC) * 8 : vbase, in);
+                   in ? vbase + slot * kv.v_row + gv * vdim + (c - KC) * 8 : vbase, in);
       }
     }
     cp_async_commit();
@@ -290,23 +291,29 @@ attention_mma_kernel(AttnShape a, const __nv_bfloat16* __restrict__ q, PagedKV k
     __syncthreads();  // the stage is loaded again two tiles on
   }
   lA = quad_sum(lA), lB = quad_sum(lB);
-  if (splits == 1) {
+  if (splits == 1 && !a.no_merge) {
     if (a.sink != nullptr) {  // exp(sink) joins the denominator; scores are in units of log2
       constexpr float kLog2e = 1.4426950408889634f;
       if (exA) lA = mA > -INFINITY ? lA + exp2_approx(a.sink[thA % a.heads] * kLog2e - mA) : 1.0f;
       if (exB) lB = mB > -INFINITY ? lB + exp2_approx(a.sink[thB % a.heads] * kLog2e - mB) : 1.0f;
     }
-    const float gA = exA && gates ? gates[thA] : 1.0f, gB = exB && gates ? gates[thB] : 1.0f;
+    const bool per_element = gates != nullptr && a.gate == KLLM_SEQ_GATE_ELEMENT;
+    const float gA = exA && gates && !per_element ? gates[thA] : 1.0f, gB = exB && gates && !per_element ? gates[thB] : 1.0f;
 #pragma unroll
     for (int nb = 0; nb < NB; ++nb) {
       const int col = nb * 8 + t4 * 2;
       if (col >= vdim) break;
+      float2 eA = make_float2(gA, gA), eB = make_float2(gB, gB);
+      if (per_element) {
+        if (exA) eA = *reinterpret_cast<const float2*>(gates + thA * vdim + col);
+        if (exB) eB = *reinterpret_cast<const float2*>(gates + thB * vdim + col);
+      }
       if (exA)
         *reinterpret_cast<__nv_bfloat162*>(out + thA * vdim + col) =
-            __floats2bfloat162_rn(o[nb][0] / lA * gA, o[nb][1] / lA * gA);
+            __floats2bfloat162_rn(o[nb][0] / lA * eA.x, o[nb][1] / lA * eA.y);
       if (exB)
         *reinterpret_cast<__nv_bfloat162*>(out + thB * vdim + col) =
-            __floats2bfloat162_rn(o[nb][2] / lB * gB, o[nb][3] / lB * gB);
+            __floats2bfloat162_rn(o[nb][2] / lB * eB.x, o[nb][3] / lB * eB.y);
     }
     return;
   }

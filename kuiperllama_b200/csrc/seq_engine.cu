@@ -8,8 +8,8 @@
 // returns them at close.  The table rows of the step's sequences are copied to the device before the kernels run.
 //
 // State.  Beside the pages, every layer run owns per-slot recurrent state in fp32: the last mixer input of a layer with a
-// token shift, the matrix state of linear attention and of the delta rule, the diagonal state of the selective scan, and
-// the last taps - 1 inputs of every short convolution.  A sequence of length 0 reads zeros instead of its slot's
+// token shift, the matrix state of linear attention, of the delta rule and of the duality mixer, the diagonal state of
+// the selective scan, and the last taps - 1 inputs of every short convolution.  A sequence of length 0 reads zeros instead of its slot's
 // memory, so slots are reused without clearing.  A run of attention through a latent keeps one row per token in its pool
 // (latent | rotated key part); its values are the head of that row.
 //
@@ -34,7 +34,14 @@
 //                  delta rule: gemm (q | k | v | beta | low-rank rows), delta_low + gemm (second low-rank products),
 //                              delta_prepare (filters, unit vectors, decays, gates), delta_rule (one kernel, or two passes
 //                              over segments with a carry between them), delta_out (per-head norm and gate)
-//                  a layer may run two mixers of different kinds on the same rows; their outputs join x with a weight each
+//                  duality:    gemm (z | x | B | C | dt rows), ssd_conv (filter + SiLU), ssd_scan (one decay per head and
+//                              token; one kernel, or scan / carry / finish over segments of long entries), ssd_out (gate,
+//                              RMS norm in parts, weight)
+//                  an attention may also rotate its queries and keys (frequencies from a table), norm them after the
+//                  rotation, gate every output element, and run as a DIFFERENTIAL attention: two maps per head over the
+//                  same values, joined by diff_merge
+//                  a layer may run two mixers of different kinds on the same rows; their outputs join x with a weight each,
+//                  each after an RMS norm of its own when the layer names one
 //     gemm         output projection
 //     resid_norm   x += N_post(y);  h = N_pre_ff(x);  router on h (softmax or sigmoid with groups): same kernel, the row
 //                  is still in shared memory
@@ -116,6 +123,8 @@ struct kllm_seq_engine {
   // more state per run and slot (fp32): the last taps - 1 inputs of the short convolutions of an attention, a selective
   // scan and a delta rule; the diagonal state of the scan [max_seqs][inner][state]; the delta rule's [max_seqs][heads][dim][vdim]
   std::vector<float*> attn_conv, ssm_conv, ssm_state, delta_conv, delta_state;
+  // the duality mixer's convolution history [max_seqs][taps - 1][channels] and state [max_seqs][heads][vdim][state]
+  std::vector<float*> ssd_conv, ssd_state;
   int32_t* table_dev = nullptr;       // [max_seqs][table_stride]
   std::vector<int32_t> table_host;
   std::vector<int32_t> free_pages;    // kept sorted descending: back() is the lowest number
@@ -163,7 +172,7 @@ struct kllm_seq_engine {
     prof_phase.push_back(phase);
   }
   // limits over the layers
-  int max_proj = 0, max_q = 0, max_att = 0, max_heads = 0, max_top = 0, max_ff = 0, max_sff = 0;
+  int max_proj = 0, max_q = 0, max_att = 0, max_gates = 0, max_ws_heads = 0, max_top = 0, max_ff = 0, max_sff = 0;
   int max_qf = 0, max_qa = 0, max_ol = 0, max_rec_a = 0, max_rec_b = 0, max_rec_c = 0;
   bool any_mixer2 = false, any_parallel_ff = false;
   bool any_shift = false, any_run_embed = false;
@@ -174,7 +183,7 @@ struct kllm_seq_engine {
     for (void* p : v_pool) if (p) cudaFree(p);
     for (float* p : shift_state) if (p) cudaFree(p);
     for (float* p : linear_state) if (p) cudaFree(p);
-    for (auto* v : {&attn_conv, &ssm_conv, &ssm_state, &delta_conv, &delta_state})
+    for (auto* v : {&attn_conv, &ssm_conv, &ssm_state, &delta_conv, &delta_state, &ssd_conv, &ssd_state})
       for (float* p : *v) if (p) cudaFree(p);
     if (table_dev) cudaFree(table_dev);
     if (pinned) cudaFreeHost(pinned);
@@ -185,6 +194,22 @@ struct kllm_seq_engine {
   }
 };
 
+// how many maps a head of this attention holds, and the shape its kernels see (heads and key heads count the maps)
+static int attn_maps(const kllm_seq_attention& a) { return a.differential ? 2 : 1; }
+static AttnShape attn_shape(const kllm_seq_attention& A) {
+  const int maps = attn_maps(A);
+  AttnShape s{};
+  s.heads = A.heads * maps, s.kv_heads = A.kv_heads * maps, s.dim = A.dim, s.vdim = A.vdim, s.scale = A.scale;
+  s.temp_coef = A.temp_coef, s.temp_every = A.temp_every, s.qk_norm = A.qk_norm, s.gate = A.gate, s.window = A.window;
+  s.sink = A.sink, s.keep_first = A.keep_first, s.softcap = A.softcap, s.v_share = maps;
+  s.no_merge = A.differential ? 1 : 0;  // the maps' key splits are joined by diff_merge
+  return s;
+}
+static int attn_proj_rows(const kllm_seq_attention& A) {
+  const AttnShape s = attn_shape(A);
+  return s.heads * A.dim + s.kv_heads * A.dim + (A.values_are_keys ? 0 : A.kv_heads * A.vdim) + gate_floats(s);
+}
+
 static bool has_cache(int kind) { return kind == KLLM_SEQ_MIXER_ATTENTION || kind == KLLM_SEQ_MIXER_LATENT; }
 
 static int validate_mixer(const kllm_seq_layer& L, int kind) {
@@ -192,15 +217,18 @@ static int validate_mixer(const kllm_seq_layer& L, int kind) {
     const kllm_seq_attention& a = L.attn;
     if (a.heads <= 0 || a.kv_heads <= 0 || a.heads % a.kv_heads || a.dim <= 0 || a.vdim <= 0 || !a.w_in || !a.w_out)
       return KLLM_E_INVALID;
-    if (a.qk_norm && (!a.q_norm_w || !a.k_norm_w)) return KLLM_E_INVALID;
+    if (a.qk_norm == KLLM_SEQ_QKNORM_WEIGHTED && (!a.q_norm_w || !a.k_norm_w)) return KLLM_E_INVALID;
+    if (a.qk_norm < 0 || a.qk_norm > KLLM_SEQ_QKNORM_UNIT || a.gate < 0 || a.gate > KLLM_SEQ_GATE_ELEMENT) return KLLM_E_INVALID;
+    // the two maps of a differential head are joined without a sink; the filtered form has one map
+    if (a.differential && (a.sink || a.values_are_keys)) return KLLM_E_UNSUPPORTED;
     if (a.vdim > 256 || a.dim > 512) return KLLM_E_UNSUPPORTED;
     if (a.window < 0 || a.keep_first < 0 || a.softcap < 0.f || a.conv_taps < 0 || a.rope_dims < 0 || a.rope_dims > a.dim ||
         (a.rope_dims & 1) || (a.rope_dims > 0 && a.rope_base <= 0.f))
       return KLLM_E_INVALID;
     if (a.values_are_keys && a.vdim != a.dim) return KLLM_E_INVALID;
     // the filtered, rotated form has its own preparation kernel: no head norms, temperature or gate there
-    const bool prep2 = a.values_are_keys || a.conv_taps > 1 || a.conv_w || a.rope_dims > 0 || a.in_bias;
-    if (prep2 && (!a.values_are_keys || a.qk_norm || a.gate || a.temp_every)) return KLLM_E_UNSUPPORTED;
+    const bool prep2 = a.values_are_keys || a.conv_taps > 1 || a.conv_w || a.in_bias;
+    if (prep2 && (!a.values_are_keys || a.qk_norm || a.gate || a.temp_every || a.rope_freq)) return KLLM_E_UNSUPPORTED;
   } else if (kind == KLLM_SEQ_MIXER_LATENT) {
     const kllm_seq_latent& a = L.latent;
     if (a.heads <= 0 || a.dim <= 0 || a.rot_dim < 0 || a.vdim <= 0 || a.q_rank <= 0 || a.kv_rank <= 0 || a.window < 0 ||
@@ -226,6 +254,13 @@ static int validate_mixer(const kllm_seq_layer& L, int kind) {
         !a.rate || !a.out_norm_w || !a.w_out)
       return KLLM_E_INVALID;
     if (a.dim > 256) return KLLM_E_UNSUPPORTED;
+  } else if (kind == KLLM_SEQ_MIXER_SSD) {
+    const kllm_seq_ssd& a = L.ssd;
+    if (a.heads <= 0 || a.vdim <= 0 || a.state <= 0 || a.groups <= 0 || a.heads % a.groups || a.conv_taps < 1 ||
+        a.norm_groups <= 0 || (a.heads * a.vdim) % a.norm_groups || !a.w_in || !a.conv_w || !a.dt_bias || !a.a || !a.d ||
+        !a.out_norm_w || !a.w_out)
+      return KLLM_E_INVALID;
+    if (a.state > 512) return KLLM_E_UNSUPPORTED;
   } else {
     return KLLM_E_UNSUPPORTED;
   }
@@ -243,7 +278,10 @@ static int validate(const kllm_seq_desc* d) {
   }
   for (int i = 0; i < d->n_layers; ++i) {
     const kllm_seq_layer& L = d->layers[i];
-    if (!L.pre_mixer.w) return KLLM_E_INVALID;
+    if (!L.pre_mixer.w && L.pre_mixer.kind != KLLM_SEQ_NORM_NONE) return KLLM_E_INVALID;
+    for (const kllm_seq_norm* n : {&L.mixer_out_norm, &L.mixer2_out_norm})
+      if (n->w && n->kind != KLLM_SEQ_NORM_RMS) return KLLM_E_UNSUPPORTED;
+    if (L.shift && L.pre_mixer.kind == KLLM_SEQ_NORM_NONE) return KLLM_E_UNSUPPORTED;
     if (int rc = validate_mixer(L, L.mixer_kind)) return rc;
     if (L.mixer2_kind != 0) {
       // the two mixers of a layer are of different kinds (a layer describes one mixer of each), and only one keeps pages
@@ -254,7 +292,7 @@ static int validate(const kllm_seq_desc* d) {
     if (L.ff_kind == KLLM_SEQ_FF_MOE) {
       const kllm_seq_moe& m = L.moe;
       if (m.experts <= 0 || m.top <= 0 || m.top > m.experts || m.ff <= 0 || !m.w_router || !m.gate_up || !m.down ||
-          (!L.pre_ff.w && !L.parallel_ff))
+          (!L.pre_ff.w && !L.parallel_ff))  // the router reads a normed row
         return KLLM_E_INVALID;
       if (m.shared_ff > 0 && (!m.shared_gate_up || !m.shared_down)) return KLLM_E_INVALID;
       if (m.act != KLLM_SEQ_ACT_SWIGLU && m.act != KLLM_SEQ_ACT_CLAMP_SWIGLU && (m.act != KLLM_SEQ_ACT_RELU2 || m.shared_ff > 0))
@@ -266,7 +304,8 @@ static int validate(const kllm_seq_desc* d) {
         return KLLM_E_INVALID;
     } else if (L.ff_kind == KLLM_SEQ_FF_DENSE) {
       const kllm_seq_dense& f = L.dense;
-      if (f.ff <= 0 || !f.up || !f.down || (!L.pre_ff.w && !L.parallel_ff)) return KLLM_E_INVALID;
+      if (f.ff <= 0 || !f.up || !f.down || (!L.pre_ff.w && L.pre_ff.kind != KLLM_SEQ_NORM_NONE && !L.parallel_ff))
+        return KLLM_E_INVALID;
       if (f.act != KLLM_SEQ_ACT_XIELU && f.act != KLLM_SEQ_ACT_RELU2 && f.act != KLLM_SEQ_ACT_RELU_GATE) return KLLM_E_UNSUPPORTED;
     } else if (L.ff_kind != KLLM_SEQ_FF_NONE) {
       return KLLM_E_UNSUPPORTED;
@@ -316,6 +355,7 @@ extern "C" int kllm_seq_create(const kllm_seq_desc* desc, void* stream, kllm_seq
     const kllm_seq_layer& L = e->layers[e->run_layer[r]];
     void *k = nullptr, *v = nullptr;
     float *sh = nullptr, *ls = nullptr, *ac = nullptr, *sc = nullptr, *ss = nullptr, *dc = nullptr, *ds = nullptr;
+    float *dual_conv = nullptr, *dual_state = nullptr;
     const size_t tokens = static_cast<size_t>(e->n_pages) * e->page;
     const size_t slots = static_cast<size_t>(desc->max_seqs);
     bool ok = true;
@@ -324,7 +364,7 @@ extern "C" int kllm_seq_create(const kllm_seq_desc* desc, void* stream, kllm_seq
       if (!ok) break;
       if (kind == KLLM_SEQ_MIXER_ATTENTION) {
         const kllm_seq_attention& a = L.attn;
-        ok = cudaMalloc(&k, tokens * a.kv_heads * a.dim * es) == cudaSuccess &&
+        ok = cudaMalloc(&k, tokens * a.kv_heads * attn_maps(a) * a.dim * es) == cudaSuccess &&
              cudaMalloc(&v, tokens * a.kv_heads * a.vdim * es) == cudaSuccess &&
              f32(&ac, a.conv_taps > 1 ? slots * (a.conv_taps - 1) * (a.heads + a.kv_heads) * a.dim : 0);
       } else if (kind == KLLM_SEQ_MIXER_LATENT) {
@@ -337,6 +377,10 @@ extern "C" int kllm_seq_create(const kllm_seq_desc* desc, void* stream, kllm_seq
         const kllm_seq_delta& a = L.delta;
         ok = f32(&dc, slots * (a.conv_taps - 1) * (2 * a.kv_heads * a.dim + a.heads * a.vdim)) &&
              f32(&ds, slots * a.heads * a.dim * a.vdim);
+      } else if (kind == KLLM_SEQ_MIXER_SSD) {
+        const kllm_seq_ssd& a = L.ssd;
+        ok = f32(&dual_conv, slots * (a.conv_taps - 1) * ssd_conv_channels(a)) &&
+             f32(&dual_state, slots * a.heads * a.vdim * a.state);
       }
     }
     if (ok && L.shift) ok = cudaMalloc(&sh, static_cast<size_t>(desc->max_seqs) * desc->width * sizeof(float)) == cudaSuccess;
@@ -346,6 +390,7 @@ extern "C" int kllm_seq_create(const kllm_seq_desc* desc, void* stream, kllm_seq
     e->linear_state.push_back(ls);
     e->attn_conv.push_back(ac), e->ssm_conv.push_back(sc), e->ssm_state.push_back(ss);
     e->delta_conv.push_back(dc), e->delta_state.push_back(ds);
+    e->ssd_conv.push_back(dual_conv), e->ssd_state.push_back(dual_state);
     if (!ok) {
       delete e;
       return static_cast<int>(cudaErrorMemoryAllocation);
@@ -363,11 +408,10 @@ extern "C" int kllm_seq_create(const kllm_seq_desc* desc, void* stream, kllm_seq
     for (int kind : {L.mixer_kind, L.mixer2_kind}) {
       if (kind == KLLM_SEQ_MIXER_ATTENTION) {
         const kllm_seq_attention& a = L.attn;
-        e->max_proj = std::max(e->max_proj, a.heads * a.dim + a.kv_heads * (a.dim + (a.values_are_keys ? 0 : a.vdim)) +
-                                                (a.gate ? a.heads : 0));
-        e->max_q = std::max(e->max_q, a.heads * a.dim);
+        e->max_proj = std::max(e->max_proj, attn_proj_rows(a));
+        e->max_q = std::max(e->max_q, a.heads * attn_maps(a) * a.dim);
         e->max_att = std::max(e->max_att, a.heads * a.vdim);
-        e->max_heads = std::max(e->max_heads, a.heads);
+        e->max_gates = std::max(e->max_gates, gate_floats(attn_shape(a)));
       } else if (kind == KLLM_SEQ_MIXER_LATENT) {
         const kllm_seq_latent& a = L.latent;
         e->max_proj = std::max(e->max_proj, a.q_rank + a.kv_rank + a.rot_dim + a.heads);
@@ -376,7 +420,7 @@ extern "C" int kllm_seq_create(const kllm_seq_desc* desc, void* stream, kllm_seq
         e->max_qa = std::max(e->max_qa, a.heads * (a.kv_rank + a.rot_dim));
         e->max_ol = std::max(e->max_ol, a.heads * a.kv_rank);
         e->max_att = std::max(e->max_att, a.heads * a.vdim);
-        e->max_heads = std::max(e->max_heads, a.heads);
+        e->max_gates = std::max(e->max_gates, a.heads);
       } else if (kind == KLLM_SEQ_MIXER_LINEAR) {
         const kllm_seq_linear& a = L.linear;
         e->max_proj = std::max(e->max_proj, 2 * a.heads * (a.dim + a.vdim));
@@ -396,6 +440,12 @@ extern "C" int kllm_seq_create(const kllm_seq_desc* desc, void* stream, kllm_seq
         e->max_rec_b = std::max(e->max_rec_b, a.heads * a.vdim);
         e->max_rec_c = std::max(e->max_rec_c, a.heads * (a.dim + a.vdim));
         e->max_q = std::max(e->max_q, a.decay_rank + a.gate_rank);
+      } else if (kind == KLLM_SEQ_MIXER_SSD) {
+        const kllm_seq_ssd& a = L.ssd;
+        e->max_proj = std::max(e->max_proj, ssd_proj_row(a));
+        e->max_att = std::max(e->max_att, ssd_inner(a));
+        e->max_rec_a = std::max(e->max_rec_a, ssd_conv_channels(a));
+        e->max_rec_b = std::max(e->max_rec_b, ssd_inner(a));
       }
     }
     if (L.ff_kind == KLLM_SEQ_FF_DENSE) {
@@ -568,7 +618,7 @@ extern "C" int kllm_seq_step(kllm_seq_engine* e, int32_t n_entries, const int32_
   RC(e->h.reserve(Ts * W * es));
   RC(e->proj.reserve(Ts * std::max({e->max_proj, 2 * e->max_sff, W}) * 4));
   RC(e->q.reserve(Ts * std::max(1, e->max_q) * es));
-  RC(e->gates.reserve(Ts * std::max(1, e->max_heads) * 4));
+  RC(e->gates.reserve(Ts * std::max(1, e->max_gates) * 4));
   RC(e->att.reserve(Ts * std::max(e->max_att, e->max_sff) * es));
   RC(e->y.reserve(Ts * W * 4));
   RC(e->y2.reserve(Ts * W * 4));
@@ -586,7 +636,7 @@ extern "C" int kllm_seq_step(kllm_seq_engine* e, int32_t n_entries, const int32_
   for (const kllm_seq_layer& L : e->layers)
     for (int kind : {L.mixer_kind, L.mixer2_kind}) {
       AttnShape a{};
-      if (kind == KLLM_SEQ_MIXER_ATTENTION) a.heads = L.attn.heads, a.vdim = L.attn.vdim;
+      if (kind == KLLM_SEQ_MIXER_ATTENTION) a.heads = L.attn.heads * attn_maps(L.attn), a.vdim = L.attn.vdim;
       else if (kind == KLLM_SEQ_MIXER_LATENT) a.heads = L.latent.heads, a.vdim = L.latent.kv_rank;
       else continue;
       ws_bytes = std::max(ws_bytes, attention_workspace_bytes(a, T, splits));
@@ -600,6 +650,9 @@ extern "C" int kllm_seq_step(kllm_seq_engine* e, int32_t n_entries, const int32_
   for (const kllm_seq_layer& L : e->layers)
     if (L.mixer_kind == KLLM_SEQ_MIXER_DELTA || L.mixer2_kind == KLLM_SEQ_MIXER_DELTA)
       ws_bytes = std::max(ws_bytes, delta_rule_scratch_bytes(L.delta, T, n_entries, max_count));
+  for (const kllm_seq_layer& L : e->layers)
+    if (L.mixer_kind == KLLM_SEQ_MIXER_SSD || L.mixer2_kind == KLLM_SEQ_MIXER_SSD)
+      ws_bytes = std::max(ws_bytes, ssd_scan_scratch_bytes(L.ssd, T, n_entries, max_count));
   RC(e->ws.reserve(ws_bytes));
   const bool grouped = T >= kGroupedMinTokens;
   if (e->max_top > 0) {
@@ -667,11 +720,10 @@ extern "C" int kllm_seq_step(kllm_seq_engine* e, int32_t n_entries, const int32_
   auto run_mixer = [&](const kllm_seq_layer& L, int kind, int r, float* yout) -> int {
     if (kind == KLLM_SEQ_MIXER_ATTENTION) {
       const kllm_seq_attention& A = L.attn;
-      const AttnShape shape{A.heads, A.kv_heads, A.dim, A.vdim, A.scale, A.temp_coef, A.temp_every, A.qk_norm, A.gate,
-                            A.window, A.sink, 0, 0, 0, A.keep_first, A.softcap};
-      const PagedKV kv{e->k_pool[r], e->v_pool[r], e->table_dev, e->table_stride, e->page, A.kv_heads * A.dim,
+      const AttnShape shape = attn_shape(A);
+      const PagedKV kv{e->k_pool[r], e->v_pool[r], e->table_dev, e->table_stride, e->page, shape.kv_heads * A.dim,
                        A.kv_heads * A.vdim};
-      const int n_proj = A.heads * A.dim + A.kv_heads * (A.dim + (A.values_are_keys ? 0 : A.vdim)) + (A.gate ? A.heads : 0);
+      const int n_proj = attn_proj_rows(A);
       RC(gemm(dtype, e->h.p, A.w_in, proj, T, W, n_proj, st));
       e->mark(KLLM_SEQ_PHASE_IN_PROJ);
       if (A.values_are_keys) {
@@ -679,13 +731,18 @@ extern "C" int kllm_seq_step(kllm_seq_engine* e, int32_t n_entries, const int32_
                             A.rope_base};
         RC(launch_qk_conv_prepare(dtype, shape, prep, proj, step_rows, e->q.p, kv, T, st));
       } else {
-        RC(launch_qk_prepare(dtype, shape, proj, A.q_norm_w, A.k_norm_w, d.norm_eps, d_seq, d_pos, e->q.p,
+        const RopeArgs rope{A.rope_dims, A.rope_base, A.rope_freq, A.rope_mag, A.rope_pairing};
+        RC(launch_qk_prepare(dtype, shape, rope, proj, A.q_norm_w, A.k_norm_w, d.norm_eps, d_seq, d_pos, e->q.p,
                              static_cast<float*>(e->gates.p), kv, T, st));
       }
       e->mark(KLLM_SEQ_PHASE_QK_PREPARE);
       RC(launch_attention(dtype, shape, e->q.p, static_cast<const float*>(e->gates.p), kv, n_entries, d_first, d_count,
                           d_eseq, d_pos0, max_count, max_ctx, window_splits(A.keep_first > 0 ? 0 : A.window),
                           static_cast<float*>(e->ws.p), e->att.p, T, d_seq, d_pos, st));
+      if (A.differential)
+        RC(launch_diff_merge(dtype, shape, window_splits(A.keep_first > 0 ? 0 : A.window), static_cast<const float*>(e->ws.p),
+                             static_cast<const float*>(e->gates.p), A.diff_lambda, A.diff_out_scale, d.norm_eps, e->att.p, T,
+                             st));
       e->mark(KLLM_SEQ_PHASE_ATTENTION);
       RC(gemm(dtype, e->att.p, A.w_out, yout, T, A.heads * A.vdim, W, st));
       e->mark(KLLM_SEQ_PHASE_OUT_PROJ);
@@ -771,6 +828,19 @@ extern "C" int kllm_seq_step(kllm_seq_engine* e, int32_t n_entries, const int32_
                          static_cast<float*>(e->ws.p), e->att.p, st));
       e->mark(KLLM_SEQ_PHASE_ATTENTION);
       RC(gemm(dtype, e->att.p, A.w_out, yout, T, A.inner, W, st));
+      e->mark(KLLM_SEQ_PHASE_OUT_PROJ);
+    } else if (kind == KLLM_SEQ_MIXER_SSD) {
+      const kllm_seq_ssd& A = L.ssd;
+      float* xbc = static_cast<float*>(e->rec_a.p);
+      float* yr = static_cast<float*>(e->rec_b.p);
+      RC(gemm(dtype, e->h.p, A.w_in, proj, T, W, ssd_proj_row(A), st));
+      e->mark(KLLM_SEQ_PHASE_IN_PROJ);
+      RC(launch_ssd_conv(A, proj, e->ssd_conv[r], step_rows, xbc, T, st));
+      e->mark(KLLM_SEQ_PHASE_QK_PREPARE);
+      RC(launch_ssd_scan(A, proj, xbc, e->ssd_state[r], step_rows, d_eseq, max_count, T, static_cast<float*>(e->ws.p), yr, st));
+      RC(launch_ssd_out(dtype, A, yr, proj, d.norm_eps, e->att.p, T, st));
+      e->mark(KLLM_SEQ_PHASE_ATTENTION);
+      RC(gemm(dtype, e->att.p, A.w_out, yout, T, ssd_inner(A), W, st));
       e->mark(KLLM_SEQ_PHASE_OUT_PROJ);
     } else {
       const kllm_seq_delta& A = L.delta;
@@ -878,6 +948,7 @@ extern "C" int kllm_seq_step(kllm_seq_engine* e, int32_t n_entries, const int32_
     ResidNormArgs mixed{};
     mixed.y1 = y;
     if (L.mixer2_kind != 0) mixed.c1 = L.mixer_scale, mixed.y3 = y3, mixed.c3 = L.mixer2_scale;
+    mixed.n1 = nw(L.mixer_out_norm), mixed.n3 = nw(L.mixer2_out_norm);
 
     // what follows this layer run: the next run's additions and pre-norm can ride on this run's last kernel
     const bool fuse_next = r + 1 < d.n_runs && !tracing;

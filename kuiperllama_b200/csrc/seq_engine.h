@@ -56,6 +56,23 @@ struct AttnShape {
   int no_merge;     // leave the splits' partial results in the workspace: the caller merges them (latent_merge_expand)
   int keep_first;   // with a window: the first keep_first positions stay visible to every later one
   float softcap;    // score <- softcap * tanh(score / softcap) after the scale; 0: none
+  // Attention maps that share values: v_share consecutive key heads read the values of ONE value head (key head g reads
+  // value head g / v_share; the value rows hold kv_heads / v_share heads).  `heads` and `kv_heads` count the maps.  0: 1.
+  int v_share;
+};
+inline __host__ __device__ int v_share_of(const AttnShape& a) { return a.v_share > 1 ? a.v_share : 1; }
+// floats of one token's output gates: none, one per head, or one per output element (heads count maps; gates do not)
+inline __host__ __device__ int gate_floats(const AttnShape& a) {
+  const int h = a.heads / v_share_of(a);
+  return a.gate == KLLM_SEQ_GATE_ELEMENT ? h * a.vdim : (a.gate ? h : 0);
+}
+// Rotary positions on the first `dims` coordinates of every query / key head (map).
+struct RopeArgs {
+  int dims;           // 0: none
+  float base;         // angle of pair i = position * base^(-2 i / dims) ...
+  const float* freq;  // ... or position * freq[i] when given ([dims / 2] fp32)
+  float mag;          // cos and sin are multiplied by it
+  int pairing;        // KLLM_SEQ_ROPE_*
 };
 
 // The activation that joins a gate row's product g and an up row's product u (see KLLM_SEQ_ACT_*).
@@ -127,15 +144,25 @@ struct ResidNormArgs {
   const float* y3;        // further addends of the sum that joins x (with y1)
   const float* y4;
   float c1 = 1.0f, c3 = 1.0f, c4 = 1.0f;  // the coefficients of y1, y3, y4
+  NormW n1{}, n3{};  // RMS norms of y1 and y3 on their own, before the sum (w == null: none)
 };
 int launch_resid_norm(const ResidNormArgs& a, cudaStream_t s);
 
-// qkvg: [T, heads*dim + kv_heads*dim + kv_heads*vdim + (gate ? heads : 0)] fp32 (projection output).
-// Writes q [T, heads, dim] (compute type; normed, temperature applied), the key / value rows into the pages, and the
-// gates sigmoid(.) [T, heads] fp32.
-int launch_qk_prepare(int dtype, const AttnShape& a, const float* qkvg, const float* qnorm_w, const float* knorm_w,
-                      float eps, const int32_t* tok_seq, const int32_t* tok_pos, void* q, float* gates,
+// qkvg: [T, heads*dim + kv_heads*dim + (kv_heads / v_share)*vdim + gate_floats()] fp32 (projection output).
+// Writes q [T, heads, dim] (compute type; head norm, rotation, temperature applied), the key / value rows into the pages,
+// and the gates sigmoid(.) [T, gate_floats()] fp32.  qk_norm KLLM_SEQ_QKNORM_WEIGHTED norms before the rotation,
+// KLLM_SEQ_QKNORM_UNIT after it.  With v_share > 1 the projection's query rows are head by head [map 0 | map 1 ...] and q
+// is written map-major inside each group of heads that share keys -- head h, map m of key group g goes to index
+// (g * v_share + m) * rep + h % rep, rep = query heads per key head -- so that the attention kernels find the rows of one
+// key head side by side.
+int launch_qk_prepare(int dtype, const AttnShape& a, const RopeArgs& rope, const float* qkvg, const float* qnorm_w,
+                      const float* knorm_w, float eps, const int32_t* tok_seq, const int32_t* tok_pos, void* q, float* gates,
                       const PagedKV& kv, int T, cudaStream_t s);
+// Differential attention: joins the key splits of both maps of every head (a.no_merge left them in `ws`), then
+// o = a1 - lambda * a2, o / sqrt(mean(o^2) + eps) * out_scale over the head's vdim values, the output gate, and the
+// conversion: out [T, (heads / 2) * vdim] in the compute type.  `a` is the shape the attention ran with (v_share == 2).
+int launch_diff_merge(int dtype, const AttnShape& a, int splits, const float* ws, const float* gates, float lambda,
+                      float out_scale, float eps, void* out, int T, cudaStream_t s);
 
 // Causal softmax attention of the step's rows over their sequences' pages.  out [T, heads*vdim] (compute type).
 // `splits` CTAs share the keys of a row tile; partial (max, sum, unnormalised output) go through `ws`.
@@ -296,6 +323,24 @@ int launch_delta_rule(const kllm_seq_delta& m, const float* prep, float* state, 
 // out[t, h] = o[t, h] / rms(o[t, h]) * norm_w * gate[t, h] in the compute type
 int launch_delta_out(int dtype, const kllm_seq_delta& m, const float* o, const float* prep, float eps, void* out, int T,
                      cudaStream_t s);
+
+// ---- seq_ssd.cu: state-space duality (one decay per head and token, a matrix state per head) ---------------------------
+// proj [T, ssd_proj_row()] fp32: z | x | B | C | dt rows of the input projection.
+__host__ __device__ inline int ssd_inner(const kllm_seq_ssd& m) { return m.heads * m.vdim; }
+__host__ __device__ inline int ssd_conv_channels(const kllm_seq_ssd& m) { return m.heads * m.vdim + 2 * m.groups * m.state; }
+__host__ __device__ inline int ssd_proj_row(const kllm_seq_ssd& m) { return 2 * m.heads * m.vdim + 2 * m.groups * m.state + m.heads; }
+// xbc [T, ssd_conv_channels()] fp32 = silu(conv(x | B | C) + b); conv_state [slots][taps - 1][channels]
+int launch_ssd_conv(const kllm_seq_ssd& m, const float* proj, float* conv_state, const StepRows& rows, float* xbc, int T,
+                    cudaStream_t s);
+// the recurrence of every entry from its sequence's state ([slots][heads][vdim][state] fp32, zeros at position 0):
+// y [T, inner] fp32 (the skip d x included, ungated)
+// Steps with long entries walk segments of an entry in parallel through `scratch` (ssd_scan_scratch_bytes(); 0: not needed).
+size_t ssd_scan_scratch_bytes(const kllm_seq_ssd& m, int T, int n_entries, int max_count);
+int launch_ssd_scan(const kllm_seq_ssd& m, const float* proj, const float* xbc, float* state, const StepRows& rows,
+                    const int32_t* ent_seq, int max_count, int T, float* scratch, float* y, cudaStream_t s);
+// out[t] = group-wise RMS norm of y[t] * silu(z[t]) times out_norm_w, in the compute type
+int launch_ssd_out(int dtype, const kllm_seq_ssd& m, const float* y, const float* proj, float eps, void* out, int T,
+                   cudaStream_t s);
 
 // ---- seq_gemm.cu --------------------------------------------------------------------------------------------------
 // out[T, N] (fp32) = a[T, K] . w[N, K]^T, a and w in the compute type, fp32 accumulation.

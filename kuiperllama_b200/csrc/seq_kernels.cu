@@ -355,9 +355,21 @@ __global__ void resid_norm_kernel(ResidNormArgs a) {
   if (a.y1 != nullptr) {
     const float g = a.s2 ? a.s2[r] : 1.0f;
     const float c1 = a.c1, c3 = a.c3, c4 = a.c4;
+    // each mixer's output may pass an RMS norm of its own before the sum
+    float r1 = 1.0f, r3 = 1.0f;
+    if (a.n1.w != nullptr || (a.y3 != nullptr && a.n3.w != nullptr)) {
+      float q1 = 0.f, q3 = 0.f;
+      for (int i = threadIdx.x; i < W; i += blockDim.x) {
+        const float v1 = a.y1[src + i], v3 = a.y3 ? a.y3[src + i] : 0.f;
+        q1 = fmaf(v1, v1, q1), q3 = fmaf(v3, v3, q3);
+      }
+      const float inv_w = 1.0f / static_cast<float>(W);
+      if (a.n1.w != nullptr) r1 = 1.0f / sqrtf(block_sum(q1, red) * inv_w + a.eps);
+      if (a.y3 != nullptr && a.n3.w != nullptr) r3 = 1.0f / sqrtf(block_sum(q3, red) * inv_w + a.eps);
+    }
     for (int i = threadIdx.x; i < W; i += blockDim.x) {
-      float u = c1 * a.y1[src + i];
-      if (a.y3) u += c3 * a.y3[src + i];
+      float u = c1 * (a.n1.w ? a.y1[src + i] * r1 * a.n1.w[i] : a.y1[src + i]);
+      if (a.y3) u += c3 * (a.n3.w ? a.y3[src + i] * r3 * a.n3.w[i] : a.y3[src + i]);
       if (a.y2) u += g * a.y2[src + i];
       if (a.y4) u += c4 * a.y4[src + i];
       buf[i] = u;
@@ -385,14 +397,15 @@ __global__ void resid_norm_kernel(ResidNormArgs a) {
       buf[i] = v;
     }
   }
-  if (a.pre.w == nullptr) return;
+  const bool plain = a.pre.kind == KLLM_SEQ_NORM_NONE;  // the sublayer reads the row as it is
+  if (a.pre.w == nullptr && !(plain && (a.out != nullptr || a.out_f32 != nullptr))) return;
   __syncthreads();
-  float mean, rstd;
-  row_stats(buf, W, a.pre.kind, a.eps, red, mean, rstd);
+  float mean = 0.f, rstd = 1.0f;
+  if (!plain) row_stats(buf, W, a.pre.kind, a.eps, red, mean, rstd);
   const bool route = a.router.w_router != nullptr;
   if (a.out_f32 != nullptr) {  // fp32 rows for a token-shift kernel
     for (int i = threadIdx.x; i < W; i += blockDim.x)
-      a.out_f32[dst + i] = (buf[i] - mean) * rstd * a.pre.w[i] + (a.pre.b ? a.pre.b[i] : 0.f);
+      a.out_f32[dst + i] = plain ? buf[i] : (buf[i] - mean) * rstd * a.pre.w[i] + (a.pre.b ? a.pre.b[i] : 0.f);
     return;
   }
   AT* out = static_cast<AT*>(a.out) + dst;
@@ -403,7 +416,7 @@ __global__ void resid_norm_kernel(ResidNormArgs a) {
     first = a.shift.tok_pos[r] == 0;
   }
   for (int i = threadIdx.x; i < W; i += blockDim.x) {
-    float h = (buf[i] - mean) * rstd * a.pre.w[i] + (a.pre.b ? a.pre.b[i] : 0.f);
+    float h = plain ? buf[i] : (buf[i] - mean) * rstd * a.pre.w[i] + (a.pre.b ? a.pre.b[i] : 0.f);
     if (state != nullptr) {
       const float prev = first ? 0.f : state[i];
       state[i] = h;
@@ -453,43 +466,72 @@ __device__ __forceinline__ AT* page_row(AT* base, const PagedKV& kv, int seq, in
   return base + (static_cast<size_t>(page) * kv.page + pos % kv.page) * heads * dim;
 }
 
+// One warp per query / key head (per map of a head, when the heads hold several): the head's row goes through shared
+// memory -- head norm with weights (before the rotation), rotation of the first rope.dims coordinates, unit norm (after
+// it), temperature -- and leaves as a query row or as the key row of the token's page.  Angles, cos and sin are fp32.
 template <typename AT>
-__global__ void qk_prepare_kernel(AttnShape a, const float* __restrict__ qkvg, const float* __restrict__ qnorm_w,
-                                  const float* __restrict__ knorm_w, float eps, const int32_t* __restrict__ tok_seq,
-                                  const int32_t* __restrict__ tok_pos, AT* __restrict__ q, float* __restrict__ gates,
-                                  PagedKV kv) {
+__global__ void qk_prepare_kernel(AttnShape a, RopeArgs rope, const float* __restrict__ qkvg,
+                                  const float* __restrict__ qnorm_w, const float* __restrict__ knorm_w, float eps,
+                                  const int32_t* __restrict__ tok_seq, const int32_t* __restrict__ tok_pos,
+                                  AT* __restrict__ q, float* __restrict__ gates, PagedKV kv) {
+  extern __shared__ float head_rows[];  // [warps][dim]
   const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
-  const int qn = a.heads * a.dim, kn = a.kv_heads * a.dim, vn = a.kv_heads * a.vdim;
-  const int stride = qn + kn + vn + (a.gate ? a.heads : 0);
+  const int maps = v_share_of(a);
+  const int qn = a.heads * a.dim, kn = a.kv_heads * a.dim, vn = a.kv_heads / maps * a.vdim, gn = gate_floats(a);
+  const int stride = qn + kn + vn + gn;
   const float* row = qkvg + static_cast<size_t>(t) * stride;
   const int seq = tok_seq[t], pos = tok_pos[t];
   float temp = 1.0f;
   if (a.temp_every > 0) temp = 1.0f + a.temp_coef * logf(static_cast<float>((pos + 1) / a.temp_every) + 1.0f);
   AT* krow = page_row(static_cast<AT*>(kv.k), kv, seq, pos, a.kv_heads, a.dim);
-  AT* vrow = page_row(static_cast<AT*>(kv.v), kv, seq, pos, a.kv_heads, a.vdim);
+  AT* vrow = page_row(static_cast<AT*>(kv.v), kv, seq, pos, a.kv_heads / maps, a.vdim);
+  const int rep = a.heads / a.kv_heads;
+  const int rd = rope.dims, half = rd / 2;
+  const float inv_dim = 1.0f / static_cast<float>(a.dim);
+  float* hr = head_rows + warp * a.dim;
   for (int u = warp; u < a.heads + a.kv_heads; u += nw) {
     const bool is_q = u < a.heads;
     const float* src = row + (is_q ? u * a.dim : qn + (u - a.heads) * a.dim);
-    AT* dst = is_q ? q + (static_cast<size_t>(t) * a.heads + u) * a.dim : krow + (u - a.heads) * a.dim;
+    AT* dst;
+    if (is_q) {
+      // projection order: head by head, a head's maps side by side; q order: see launch_qk_prepare
+      const int h = u / maps, m = u % maps;
+      const int j = ((h / rep) * maps + m) * rep + h % rep;
+      dst = q + (static_cast<size_t>(t) * a.heads + j) * a.dim;
+    } else {
+      dst = krow + (u - a.heads) * a.dim;
+    }
     float rinv = 1.0f;
-    if (a.qk_norm) {
+    if (a.qk_norm == KLLM_SEQ_QKNORM_WEIGHTED) {
       float ss = 0.f;
-      for (int d = lane; d < a.dim; d += 32) ss += src[d] * src[d];
-      ss = warp_sum(ss);
-      rinv = 1.0f / sqrtf(ss / static_cast<float>(a.dim) + eps);
+      for (int d = lane; d < a.dim; d += 32) ss = fmaf(src[d], src[d], ss);
+      rinv = 1.0f / sqrtf(warp_sum(ss) * inv_dim + eps);
     }
     const float* nw_ = is_q ? qnorm_w : knorm_w;
-    for (int d = lane; d < a.dim; d += 32) {
-      float v = src[d];
-      if (a.qk_norm) v = v * rinv * nw_[d];
-      if (is_q) v *= temp;
-      dst[d] = from_f<AT>(v);
+    for (int d = lane; d < a.dim; d += 32) hr[d] = a.qk_norm == KLLM_SEQ_QKNORM_WEIGHTED ? src[d] * rinv * nw_[d] : src[d];
+    __syncwarp();
+    for (int i = lane; i < half; i += 32) {
+      const int d0 = rope.pairing == KLLM_SEQ_ROPE_PAIRS ? 2 * i : i, d1 = rope.pairing == KLLM_SEQ_ROPE_PAIRS ? 2 * i + 1 : i + half;
+      const float freq = rope.freq ? rope.freq[i] : powf(rope.base, -2.0f * static_cast<float>(i) / static_cast<float>(rd));
+      const float ang = static_cast<float>(pos) * freq;
+      const float co = cosf(ang) * rope.mag, si = sinf(ang) * rope.mag;
+      const float x0 = hr[d0], x1 = hr[d1];
+      hr[d0] = x0 * co - x1 * si;
+      hr[d1] = x1 * co + x0 * si;
     }
+    __syncwarp();
+    float post = is_q ? temp : 1.0f;
+    if (a.qk_norm == KLLM_SEQ_QKNORM_UNIT) {
+      float ss = 0.f;
+      for (int d = lane; d < a.dim; d += 32) ss = fmaf(hr[d], hr[d], ss);
+      post *= 1.0f / sqrtf(warp_sum(ss) * inv_dim + eps);
+    }
+    for (int d = lane; d < a.dim; d += 32) dst[d] = from_f<AT>(hr[d] * post);
+    __syncwarp();
   }
   for (int i = threadIdx.x; i < vn; i += blockDim.x) vrow[i] = from_f<AT>(row[qn + kn + i]);
-  if (a.gate)
-    for (int h = threadIdx.x; h < a.heads; h += blockDim.x)
-      gates[static_cast<size_t>(t) * a.heads + h] = 1.0f / (1.0f + expf(-row[qn + kn + vn + h]));
+  for (int i = threadIdx.x; i < gn; i += blockDim.x)
+    gates[static_cast<size_t>(t) * gn + i] = 1.0f / (1.0f + expf(-row[qn + kn + vn + i]));
 }
 
 // ---- attention ------------------------------------------------------------------------------------------------------
@@ -509,6 +551,7 @@ attention_kernel(AttnShape a, const void* __restrict__ q_, PagedKV kv, const int
                  const int32_t* __restrict__ ent_count, const int32_t* __restrict__ ent_seq,
                  const int32_t* __restrict__ ent_pos0, int splits, float* __restrict__ ws) {
   const int e = blockIdx.y / a.kv_heads, g = blockIdx.y % a.kv_heads, split = blockIdx.z;
+  const int gv = g / v_share_of(a);  // the value head this key head reads
   const int rep = a.heads / a.kv_heads;
   const int count = ent_count[e], first = ent_first[e], seq = ent_seq[e], pos0 = ent_pos0[e];
   const int n_rows = count * rep;
@@ -598,7 +641,7 @@ attention_kernel(AttnShape a, const void* __restrict__ q_, PagedKV kv, const int
             if (kj <= pmax) {
               const size_t slot = static_cast<size_t>(table[kj / kv.page]) * kv.page + kj % kv.page;
               if (c < kc) VecOf<AT>::load(kbase + slot * kv.k_row + g * a.dim + c * V, f[u]);
-              else VecOf<AT>::load(vbase + slot * kv.v_row + g * a.vdim + (c - kc) * V, f[u]);
+              else VecOf<AT>::load(vbase + slot * kv.v_row + gv * a.vdim + (c - kc) * V, f[u]);
             }
           }
         }
@@ -624,7 +667,7 @@ attention_kernel(AttnShape a, const void* __restrict__ q_, PagedKV kv, const int
       if (kj <= pmax) {
         const size_t slot = static_cast<size_t>(table[kj / kv.page]) * kv.page + kj % kv.page;
         const AT* ksrc = kbase + slot * kv.k_row + g * a.dim;
-        const AT* vsrc = vbase + slot * kv.v_row + g * a.vdim;
+        const AT* vsrc = vbase + slot * kv.v_row + gv * a.vdim;
         for (int d = lane; d < dk; d += 32) kd[d] = d < a.dim ? to_f(ksrc[d]) : 0.f;
         for (int d = lane; d < a.vdim; d += 32) vd[d] = to_f(vsrc[d]);
       } else {
@@ -737,8 +780,8 @@ attention_kernel(AttnShape a, const void* __restrict__ q_, PagedKV kv, const int
 
 template <typename AT>
 __global__ void attention_merge_kernel(int heads, int vdim, int splits, const float* __restrict__ ws,
-                                       const float* __restrict__ gates, const float* __restrict__ sink, int out_f32,
-                                       void* __restrict__ out_) {
+                                       const float* __restrict__ gates, int gate_kind, const float* __restrict__ sink,
+                                       int out_f32, void* __restrict__ out_) {
   const size_t th = blockIdx.x;  // t * heads + h
   const int pstride = vdim + 2;
   const float* p = ws + th * splits * pstride;
@@ -749,15 +792,61 @@ __global__ void attention_merge_kernel(int heads, int vdim, int splits, const fl
     const float m = p[s * pstride];
     if (m > -INFINITY) L += p[s * pstride + 1] * expf(m - M);
   }
-  const float gate = gates ? gates[th] : 1.0f;
+  const bool per_element = gates != nullptr && gate_kind == KLLM_SEQ_GATE_ELEMENT;
+  const float head_gate = gates && !per_element ? gates[th] : 1.0f;
   for (int d = threadIdx.x; d < vdim; d += blockDim.x) {
     float o = 0.f;
     for (int s = 0; s < splits; ++s) {
       const float m = p[s * pstride];
       if (m > -INFINITY) o += p[s * pstride + 2 + d] * expf(m - M);
     }
+    const float gate = per_element ? gates[th * vdim + d] : head_gate;
     if (out_f32) static_cast<float*>(out_)[th * vdim + d] = o / L * gate;
     else static_cast<AT*>(out_)[th * vdim + d] = from_f<AT>(o / L * gate);
+  }
+}
+
+// Differential attention.  One CTA per (token, head): the key splits of the head's two maps are joined (each map has a
+// softmax of its own), o = a1 - lambda * a2, then o / sqrt(mean(o^2) + eps) * out_scale over the head's values and the
+// output gate.  The maps of head h (key group g = h / rep) lie at attention heads (2 g + m) * rep + h % rep.
+template <typename AT>
+__global__ void diff_merge_kernel(int heads, int rep, int vdim, int splits, const float* __restrict__ ws,
+                                  const float* __restrict__ gates, int gate_kind, float lambda, float out_scale, float eps,
+                                  AT* __restrict__ out) {
+  extern __shared__ float orow[];  // [vdim]
+  __shared__ float red[33];
+  const int t = blockIdx.x / heads, h = blockIdx.x % heads;
+  const int pstride = vdim + 2;
+  const float* p[2];
+  float M[2], L[2];
+  for (int m = 0; m < 2; ++m) {
+    const size_t th = static_cast<size_t>(t) * heads * 2 + ((h / rep) * 2 + m) * rep + h % rep;
+    p[m] = ws + th * splits * pstride;
+    M[m] = -INFINITY, L[m] = 0.f;
+    for (int s = 0; s < splits; ++s) M[m] = fmaxf(M[m], p[m][s * pstride]);
+    for (int s = 0; s < splits; ++s) {
+      const float mm = p[m][s * pstride];
+      if (mm > -INFINITY) L[m] += p[m][s * pstride + 1] * expf(mm - M[m]);
+    }
+  }
+  float ss = 0.f;
+  for (int d = threadIdx.x; d < vdim; d += blockDim.x) {
+    float o[2] = {0.f, 0.f};
+    for (int m = 0; m < 2; ++m)
+      for (int s = 0; s < splits; ++s) {
+        const float mm = p[m][s * pstride];
+        if (mm > -INFINITY) o[m] += p[m][s * pstride + 2 + d] * expf(mm - M[m]);
+      }
+    const float v = o[0] / L[0] - lambda * (o[1] / L[1]);
+    orow[d] = v;
+    ss = fmaf(v, v, ss);
+  }
+  const float rinv = out_scale / sqrtf(block_sum(ss, red) / static_cast<float>(vdim) + eps);
+  const size_t th = static_cast<size_t>(t) * heads + h;
+  const float head_gate = gates && gate_kind == KLLM_SEQ_GATE_HEAD ? gates[th] : 1.0f;
+  for (int d = threadIdx.x; d < vdim; d += blockDim.x) {
+    const float gate = gates && gate_kind == KLLM_SEQ_GATE_ELEMENT ? gates[th * vdim + d] : head_gate;
+    out[th * vdim + d] = from_f<AT>(orow[d] * rinv * gate);
   }
 }
 
@@ -978,13 +1067,31 @@ int launch_resid_norm(const ResidNormArgs& a, cudaStream_t s) {
   return done();
 }
 
-int launch_qk_prepare(int dtype, const AttnShape& a, const float* qkvg, const float* qnorm_w, const float* knorm_w,
-                      float eps, const int32_t* tok_seq, const int32_t* tok_pos, void* q, float* gates,
+int launch_qk_prepare(int dtype, const AttnShape& a, const RopeArgs& rope_, const float* qkvg, const float* qnorm_w,
+                      const float* knorm_w, float eps, const int32_t* tok_seq, const int32_t* tok_pos, void* q, float* gates,
                       const PagedKV& kv, int T, cudaStream_t s) {
-  // a warp per head: few tokens get as many warps as there are query and key heads
-  const int threads = T <= 64 ? std::min(1024, 32 * std::max(4, a.heads + a.kv_heads)) : 128;
-  KLLM_SEQ_DISPATCH(dtype, (qk_prepare_kernel<AT><<<T, threads, 0, s>>>(a, qkvg, qnorm_w, knorm_w, eps, tok_seq, tok_pos,
-                                                                    static_cast<AT*>(q), gates, kv)));
+  RopeArgs rope = rope_;
+  if (rope.mag == 0.f) rope.mag = 1.0f;
+  if (rope.dims < 0 || (rope.dims & 1) || rope.dims > a.dim || a.kv_heads % v_share_of(a) || a.heads % v_share_of(a) ||
+      a.dim > 512)
+    return KLLM_E_INVALID;
+  // a warp per head: few tokens get as many warps as there are query and key heads; a head's row lives in shared memory
+  int warps = T <= 64 ? std::min(32, std::max(4, a.heads + a.kv_heads)) : 4;
+  warps = std::max(1, std::min(warps, 48 * 1024 / (4 * a.dim)));
+  const size_t smem = static_cast<size_t>(warps) * a.dim * sizeof(float);
+  KLLM_SEQ_DISPATCH(dtype, (qk_prepare_kernel<AT><<<T, 32 * warps, smem, s>>>(a, rope, qkvg, qnorm_w, knorm_w, eps, tok_seq,
+                                                                             tok_pos, static_cast<AT*>(q), gates, kv)));
+  return done();
+}
+
+int launch_diff_merge(int dtype, const AttnShape& a, int splits, const float* ws, const float* gates, float lambda,
+                      float out_scale, float eps, void* out, int T, cudaStream_t s) {
+  if (v_share_of(a) != 2 || a.heads % 2 || a.kv_heads % 2 || a.sink != nullptr) return KLLM_E_UNSUPPORTED;
+  const int heads = a.heads / 2;
+  const int threads = a.vdim <= 64 ? 64 : 128;
+  KLLM_SEQ_DISPATCH(dtype, (diff_merge_kernel<AT><<<T * heads, threads, a.vdim * sizeof(float), s>>>(
+                               heads, a.heads / a.kv_heads, a.vdim, splits, ws, a.gate ? gates : nullptr, a.gate, lambda,
+                               out_scale, eps, static_cast<AT*>(out))));
   return done();
 }
 
@@ -1040,7 +1147,7 @@ int launch_attention(int dtype, const AttnShape& a, const void* q, const float* 
   if (attention_mma_usable(dtype, a, max_count)) {
     rc = launch_attention_mma(a, q, gates, kv, n_entries, ent_first, ent_count, ent_seq, ent_pos0, max_count, splits, ws,
                               out, s);
-    if (rc || splits == 1) return rc;
+    if (rc || (splits == 1 && !a.no_merge)) return rc;
   } else {
 #define KLLM_ATTN_C(c)                                                                                              \
   KLLM_SEQ_DISPATCH(dtype, (rc = launch_attention_c<AT, c>(a, q, kv, n_entries, ent_first, ent_count, ent_seq, ent_pos0, \
@@ -1055,8 +1162,8 @@ int launch_attention(int dtype, const AttnShape& a, const void* q, const float* 
   }
   if (rc || a.no_merge) return rc;
   KLLM_SEQ_DISPATCH(dtype, (attention_merge_kernel<AT><<<T * a.heads, 64, 0, s>>>(a.heads, a.vdim, splits, ws,
-                                                                                 a.gate ? gates : nullptr, a.sink, a.out_f32,
-                                                                                 out)));
+                                                                                 a.gate ? gates : nullptr, a.gate, a.sink,
+                                                                                 a.out_f32, out)));
   return done();
 }
 

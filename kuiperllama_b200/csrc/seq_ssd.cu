@@ -1,0 +1,321 @@
+// State-space duality mixer of the sequence-batch engine (KLLM_SEQ_MIXER_SSD): a selective scan whose decay is one number
+// per head and token, with a matrix state per head.
+//
+//   ssd_conv   x | B | C channels of the input projection through a short causal convolution (state: the last taps - 1
+//              inputs, see seq_rows.cuh) and SiLU
+//   ssd_scan   step sizes dt = softplus(. + dt_bias), decays exp(a dt), and per head the recurrence
+//              S <- exp(a dt) S + dt B x^T,  y = S^T C + d x   over the rows of every entry, from the sequence's state
+//   ssd_out    y * silu(z), RMS norm in equal parts of the inner width, weight, conversion to the compute type
+//
+// Everything here is fp32; only ssd_out's result (the input of the output projection) is in the compute type.
+//
+// State layout: [slots][heads][vdim][state] -- the `state` coordinates of one value column lie side by side, because the
+// lanes that share a column hold them interleaved (lane l: l, l + L, l + 2 L, ...).
+//
+// Long entries.  The recurrence is linear in S, so an entry is cut into segments of kSsdSeg rows that are walked at the
+// same time, each from an empty state (the first from the sequence's): with c_t the sum of a dt from the segment's start
+// to row t, the true output is y_t = y'_t + exp(c_t) S_start^T C_t, y' the segment's own walk.
+//   ssd_scan_kernel<1>   the segment's own walk: y', c_t of every row, the segment's last S' and c
+//   ssd_carry_kernel     S_start of every segment, one after the other; the sequence's new state
+//   ssd_scan_kernel<2>   y += exp(c_t) S_start^T C_t
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cstdint>
+
+#include "seq_engine.h"
+#include "seq_rows.cuh"
+
+namespace kllm {
+namespace seq {
+namespace {
+
+constexpr unsigned kAll = 0xffffffffu;
+constexpr int kSsdThreads = 128;
+constexpr int kSsdRows = 16;          // state coordinates of a column per lane, at most
+constexpr int kSsdSeg = 128;          // rows of a segment when long entries are walked in parallel
+constexpr int kSsdParallelFrom = 256; // entries longer than this are cut into segments
+
+template <typename AT> __device__ __forceinline__ AT from_f(float v);
+template <> __device__ __forceinline__ float from_f<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float siluf(float z) { return z / (1.0f + expf(-z)); }
+__device__ __forceinline__ float softplusf(float z) { return z > 20.0f ? z : log1pf(expf(z)); }
+
+__global__ void ssd_conv_kernel(kllm_seq_ssd m, const float* __restrict__ proj, float* __restrict__ conv_state, StepRows rows,
+                                float* __restrict__ xbc) {
+  const int taps = m.conv_taps;
+  const RowPlace p = place_row(rows, blockIdx.x, taps);
+  if (p.n_here == 0) return;
+  const int hist = taps - 1, C = ssd_conv_channels(m), P = ssd_proj_row(m);
+  const float* in = proj + ssd_inner(m);  // the filtered channels follow the z rows
+  float* st = hist > 0 ? conv_state + static_cast<size_t>(p.seq) * hist * C : nullptr;
+  const int c0 = blockIdx.y * blockDim.x, c = c0 + threadIdx.x;
+  for (int jj = 0; jj < p.n_here; ++jj) {
+    const int t = blockIdx.x + jj, pos = p.pos0 + p.j0 + jj;
+    if (c < C)
+      xbc[static_cast<size_t>(t) * C + c] =
+          siluf(conv_at(in, P, c, C, taps, m.conv_w, nullptr, st, p, pos) + (m.conv_b ? m.conv_b[c] : 0.f));
+  }
+  // the thread that read a channel's old state is the one that writes its new one
+  if (p.j0 == 0 && hist > 0) conv_state_write(in, P, C, taps, nullptr, st, p, c0, min(static_cast<int>(blockDim.x), C - c0));
+}
+
+struct SsdScratch {
+  float* cum;   // [T][heads]: c_t
+  float* send;  // [segments][heads][vdim][state]: a segment's last S', then its S_start
+  float* cend;  // [segments][heads]: a segment's last c
+};
+__host__ __device__ inline int ssd_segment_id(int first, int e, int seg) { return first / kSsdSeg + e + seg; }
+
+// One CTA: one entry (MODE 0) or one segment of an entry (MODE 1, 2), one head, COLS = kSsdThreads / L value columns.  L
+// lanes share a column; lane l keeps the state coordinates l, l + L, ... of its column in registers.  Chunks of rows are
+// staged in shared memory (B, C, the columns' x, dt and the decay), then walked one row after the other; only the read-out's
+// dot product is joined over the L lanes.
+template <int MODE>
+__global__ void __launch_bounds__(kSsdThreads)
+ssd_scan_kernel(kllm_seq_ssd m, int L, int chunk, int segs_max, const float* __restrict__ proj, const float* __restrict__ xbc,
+                float* __restrict__ state, StepRows rows, const int32_t* __restrict__ ent_seq, float* __restrict__ y,
+                SsdScratch sc) {
+  const int e = MODE == 0 ? blockIdx.z : blockIdx.z / segs_max, seg = MODE == 0 ? 0 : blockIdx.z % segs_max;
+  const int e_first = rows.ent_first[e], e_count = rows.ent_count[e], pos0 = rows.ent_pos0[e], seq = ent_seq[e];
+  if (MODE != 0 && seg * kSsdSeg >= e_count) return;
+  if (MODE == 2 && seg == 0) return;  // the first segment started from the true state
+  const int first = MODE == 0 ? e_first : e_first + seg * kSsdSeg;
+  const int count = MODE == 0 ? e_count : min(kSsdSeg, e_count - seg * kSsdSeg);
+  const int h = blockIdx.y, N = m.state, V = m.vdim, inner = ssd_inner(m);
+  const int COLS = kSsdThreads / L;
+  const int lane = threadIdx.x % L, col = threadIdx.x / L, pcol = blockIdx.x * COLS + col;
+  const bool live = pcol < V;
+  const int g = h / (m.heads / m.groups);
+  const int C = ssd_conv_channels(m), P = ssd_proj_row(m);
+  const int b_off = inner + g * N, c_off = inner + m.groups * N + g * N, dt_off = 2 * inner + 2 * m.groups * N + h;
+  const float rate = m.a[h], skip = m.d[h], dt_bias = m.dt_bias[h];
+
+  extern __shared__ float sm[];
+  float* B_s = sm;                    // [chunk][N]
+  float* C_s = B_s + chunk * N;       // [chunk][N]
+  float* x_s = C_s + chunk * N;       // [chunk][COLS]
+  float* y_s = x_s + chunk * COLS;    // [chunk][COLS]
+  float* dt_s = y_s + chunk * COLS;   // [chunk]
+  float* dec_s = dt_s + chunk;        // [chunk]: exp(a dt)  (MODE 2: exp(c_t))
+  float* cum_s = dec_s + chunk;       // [chunk]: c_t
+
+  float S[kSsdRows];
+  const size_t sid = MODE == 0 ? 0 : ssd_segment_id(e_first, e, seg);
+  {
+    const float* src = MODE == 2 ? sc.send + ((sid * m.heads + h) * V + (live ? pcol : 0)) * N
+                                 : state + ((static_cast<size_t>(seq) * m.heads + h) * V + (live ? pcol : 0)) * N;
+    const bool from_state = MODE == 2 || (pos0 > 0 && seg == 0);
+#pragma unroll
+    for (int k = 0; k < kSsdRows; ++k) {
+      const int n = lane + L * k;
+      S[k] = live && n < N && from_state ? src[n] : 0.f;
+    }
+  }
+  float cum = 0.f;  // the sum of a dt since the segment's start (the same in every thread)
+  for (int r0 = 0; r0 < count; r0 += chunk) {
+    const int nr = min(chunk, count - r0);
+    __syncthreads();
+    for (int i = threadIdx.x; i < nr * N; i += kSsdThreads) {
+      const size_t row = static_cast<size_t>(first + r0 + i / N) * C;
+      if (MODE != 2) B_s[i] = xbc[row + b_off + i % N];
+      C_s[i] = xbc[row + c_off + i % N];
+    }
+    if (MODE != 2)
+      for (int i = threadIdx.x; i < nr * COLS; i += kSsdThreads) {
+        const int pc = blockIdx.x * COLS + i % COLS;
+        x_s[i] = pc < V ? xbc[static_cast<size_t>(first + r0 + i / COLS) * C + h * V + pc] : 0.f;
+      }
+    if (threadIdx.x < nr) {
+      const size_t row = static_cast<size_t>(first + r0 + threadIdx.x);
+      if (MODE == 2) {
+        dec_s[threadIdx.x] = expf(sc.cum[row * m.heads + h]);
+      } else {
+        const float dt = softplusf(proj[row * P + dt_off] + dt_bias);
+        dt_s[threadIdx.x] = dt;
+        dec_s[threadIdx.x] = expf(rate * dt);
+      }
+    }
+    __syncthreads();
+    if (MODE == 1 && threadIdx.x == 0) {
+      float c = cum;
+      for (int r = 0; r < nr; ++r) c = fmaf(rate, dt_s[r], c), cum_s[r] = c;
+    }
+    for (int r = 0; r < nr; ++r) {
+      const float dec = dec_s[r];
+      const float* Bn = B_s + r * N;
+      const float* Cn = C_s + r * N;
+      float acc = 0.f;
+      if (MODE == 2) {
+#pragma unroll
+        for (int k = 0; k < kSsdRows; ++k) {
+          const int n = lane + L * k;
+          if (n < N) acc = fmaf(S[k], Cn[n], acc);
+        }
+      } else {
+        const float dx = dt_s[r] * x_s[r * COLS + col];
+#pragma unroll
+        for (int k = 0; k < kSsdRows; ++k) {
+          const int n = lane + L * k;
+          if (n < N) {
+            S[k] = fmaf(dec, S[k], dx * Bn[n]);
+            acc = fmaf(S[k], Cn[n], acc);
+          }
+        }
+      }
+      for (int o = L >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(kAll, acc, o);
+      if (lane == 0) y_s[r * COLS + col] = MODE == 2 ? dec * acc : fmaf(skip, x_s[r * COLS + col], acc);
+    }
+    if (MODE == 1)
+      for (int r = 0; r < nr; ++r) cum = fmaf(rate, dt_s[r], cum);
+    __syncthreads();
+    for (int i = threadIdx.x; i < nr * COLS; i += kSsdThreads) {
+      const int pc = blockIdx.x * COLS + i % COLS;
+      if (pc >= V) continue;
+      const size_t at = static_cast<size_t>(first + r0 + i / COLS) * inner + h * V + pc;
+      if (MODE == 2) y[at] += y_s[i];
+      else y[at] = y_s[i];
+    }
+    if (MODE == 1 && blockIdx.x == 0 && threadIdx.x < nr)
+      sc.cum[static_cast<size_t>(first + r0 + threadIdx.x) * m.heads + h] = cum_s[threadIdx.x];
+  }
+  if (MODE == 2) return;
+  float* dst = MODE == 1 ? sc.send + ((sid * m.heads + h) * V + (live ? pcol : 0)) * N
+                         : state + ((static_cast<size_t>(seq) * m.heads + h) * V + (live ? pcol : 0)) * N;
+  if (MODE == 1 && blockIdx.x == 0 && threadIdx.x == 0) sc.cend[sid * m.heads + h] = cum;
+#pragma unroll
+  for (int k = 0; k < kSsdRows; ++k) {
+    const int n = lane + L * k;
+    if (live && n < N) dst[n] = S[k];
+  }
+}
+
+// One thread per (entry, head, value column, state coordinate): the start state of every segment after the first, and the
+// sequence's new state.
+__global__ void ssd_carry_kernel(kllm_seq_ssd m, float* __restrict__ state, StepRows rows, const int32_t* __restrict__ ent_seq,
+                                 SsdScratch sc) {
+  const int e = blockIdx.y;
+  const size_t per = static_cast<size_t>(m.heads) * m.vdim * m.state;
+  const size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= per) return;
+  const int first = rows.ent_first[e], count = rows.ent_count[e];
+  const int segs = (count + kSsdSeg - 1) / kSsdSeg;
+  const int h = static_cast<int>(i / (static_cast<size_t>(m.vdim) * m.state));
+  float carry = sc.send[ssd_segment_id(first, e, 0) * per + i];  // the first segment started from the sequence's state
+  for (int sg = 1; sg < segs; ++sg) {
+    const size_t sid = ssd_segment_id(first, e, sg);
+    const float own = sc.send[sid * per + i];
+    sc.send[sid * per + i] = carry;
+    carry = fmaf(expf(sc.cend[sid * m.heads + h]), carry, own);
+  }
+  state[static_cast<size_t>(ent_seq[e]) * per + i] = carry;
+}
+
+// One CTA per (token, part of the norm): the part's gated values, their root mean square, the weight.
+template <typename AT>
+__global__ void ssd_out_kernel(kllm_seq_ssd m, const float* __restrict__ y, const float* __restrict__ proj, float eps,
+                               AT* __restrict__ out) {
+  __shared__ float red[33];
+  const int t = blockIdx.x, part = blockIdx.y, inner = ssd_inner(m), n = inner / m.norm_groups, P = ssd_proj_row(m);
+  const float* yr = y + static_cast<size_t>(t) * inner + part * n;
+  const float* zr = proj + static_cast<size_t>(t) * P + part * n;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const float v = yr[i] * siluf(zr[i]);
+    ss = fmaf(v, v, ss);
+  }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(kAll, ss, o);
+  if (lane == 0) red[warp] = ss;
+  __syncthreads();
+  float tot = 0.f;
+  for (int i = 0; i < nw; ++i) tot += red[i];
+  const float rinv = 1.0f / sqrtf(tot / static_cast<float>(n) + eps);
+  const float* w = m.out_norm_w + part * n;
+  AT* o = out + static_cast<size_t>(t) * inner + part * n;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) o[i] = from_f<AT>(yr[i] * siluf(zr[i]) * rinv * w[i]);
+}
+
+inline int done() {
+  count_launch();
+  return cuda_rc(cudaGetLastError());
+}
+
+// lanes that share a column: the smallest power of two that leaves each at most kSsdRows state coordinates
+inline int ssd_lanes(int state) {
+  int L = 1;
+  while (L * kSsdRows < state) L *= 2;
+  return L;
+}
+
+}  // namespace
+
+int launch_ssd_conv(const kllm_seq_ssd& m, const float* proj, float* conv_state, const StepRows& rows, float* xbc, int T,
+                    cudaStream_t s) {
+  if (m.conv_taps < 1 || (m.conv_taps > 1 && !conv_state)) return KLLM_E_INVALID;
+  const int threads = 256;
+  const dim3 grid(T, (ssd_conv_channels(m) + threads - 1) / threads);
+  ssd_conv_kernel<<<grid, threads, 0, s>>>(m, proj, conv_state, rows, xbc);
+  return done();
+}
+
+size_t ssd_scan_scratch_bytes(const kllm_seq_ssd& m, int T, int n_entries, int max_count) {
+  if (max_count <= kSsdParallelFrom) return 0;
+  const size_t segs = static_cast<size_t>(T) / kSsdSeg + n_entries + 1;
+  return (static_cast<size_t>(T) * m.heads + segs * m.heads * (static_cast<size_t>(m.vdim) * m.state + 1)) * sizeof(float);
+}
+
+int launch_ssd_scan(const kllm_seq_ssd& m, const float* proj, const float* xbc, float* state, const StepRows& rows,
+                    const int32_t* ent_seq, int max_count, int T, float* scratch, float* y, cudaStream_t s) {
+  if (m.state > 32 * kSsdRows || m.heads % m.groups) return KLLM_E_UNSUPPORTED;
+  const int L = ssd_lanes(m.state);
+  const int COLS = kSsdThreads / L;
+  const bool segments = max_count > kSsdParallelFrom && scratch != nullptr;
+  const int longest = segments ? kSsdSeg : max_count;
+  auto smem_for = [&](int chunk) {
+    return static_cast<size_t>(chunk) * (2 * m.state + 2 * COLS + 3) * sizeof(float);
+  };
+  int chunk = 32;
+  while (chunk > 1 && (smem_for(chunk) > 48 * 1024 || chunk / 2 >= longest)) chunk /= 2;
+  if (smem_for(chunk) > 48 * 1024) return KLLM_E_UNSUPPORTED;
+  const unsigned blocks = (m.vdim + COLS - 1) / COLS;
+  if (!segments) {
+    const dim3 grid(blocks, m.heads, rows.n_entries);
+    ssd_scan_kernel<0><<<grid, kSsdThreads, smem_for(chunk), s>>>(m, L, chunk, 1, proj, xbc, state, rows, ent_seq, y,
+                                                                 SsdScratch{});
+    return done();
+  }
+  const size_t segs = static_cast<size_t>(T) / kSsdSeg + rows.n_entries + 1;
+  SsdScratch sc;
+  sc.cum = scratch;
+  sc.send = sc.cum + static_cast<size_t>(T) * m.heads;
+  sc.cend = sc.send + segs * m.heads * m.vdim * m.state;
+  const int segs_max = (max_count + kSsdSeg - 1) / kSsdSeg;
+  const dim3 grid(blocks, m.heads, rows.n_entries * segs_max);
+  ssd_scan_kernel<1><<<grid, kSsdThreads, smem_for(chunk), s>>>(m, L, chunk, segs_max, proj, xbc, state, rows, ent_seq, y, sc);
+  count_launch();
+  const size_t per = static_cast<size_t>(m.heads) * m.vdim * m.state;
+  const dim3 cgrid(static_cast<unsigned>((per + 127) / 128), rows.n_entries);
+  ssd_carry_kernel<<<cgrid, 128, 0, s>>>(m, state, rows, ent_seq, sc);
+  count_launch();
+  ssd_scan_kernel<2><<<grid, kSsdThreads, smem_for(chunk), s>>>(m, L, chunk, segs_max, proj, xbc, state, rows, ent_seq, y, sc);
+  return done();
+}
+
+int launch_ssd_out(int dtype, const kllm_seq_ssd& m, const float* y, const float* proj, float eps, void* out, int T,
+                   cudaStream_t s) {
+  if (m.norm_groups <= 0 || ssd_inner(m) % m.norm_groups) return KLLM_E_INVALID;
+  const int n = ssd_inner(m) / m.norm_groups;
+  const int threads = n >= 1024 ? 256 : 128;
+  const dim3 grid(T, m.norm_groups);
+  if (dtype == KLLM_SEQ_F32) ssd_out_kernel<float><<<grid, threads, 0, s>>>(m, y, proj, eps, static_cast<float*>(out));
+  else if (dtype == KLLM_SEQ_BF16)
+    ssd_out_kernel<__nv_bfloat16><<<grid, threads, 0, s>>>(m, y, proj, eps, static_cast<__nv_bfloat16*>(out));
+  else return KLLM_E_INVALID;
+  return done();
+}
+
+}  // namespace seq
+}  // namespace kllm
