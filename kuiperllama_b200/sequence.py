@@ -26,7 +26,9 @@ class Attention(ctypes.Structure):
                 ("w_in", c_void_p), ("q_norm_w", c_void_p), ("k_norm_w", c_void_p), ("w_out", c_void_p),
                 ("window", c_int32), ("keep_first", c_int32), ("softcap", c_float), ("sink", c_void_p),
                 ("in_bias", c_void_p), ("conv_taps", c_int32), ("conv_w", c_void_p), ("rope_dims", c_int32),
-                ("rope_base", c_float), ("rope_pairing", c_int32), ("values_are_keys", c_int32)]
+                ("rope_base", c_float), ("rope_pairing", c_int32), ("values_are_keys", c_int32),
+                ("rope_freq", c_void_p), ("rope_mag", c_float), ("differential", c_int32), ("diff_lambda", c_float),
+                ("diff_out_scale", c_float)]
 
 
 class Moe(ctypes.Structure):
@@ -68,11 +70,18 @@ class Delta(ctypes.Structure):
                 ("out_norm_w", c_void_p), ("w_out", c_void_p)]
 
 
+class Ssd(ctypes.Structure):
+    _fields_ = [("heads", c_int32), ("vdim", c_int32), ("state", c_int32), ("groups", c_int32), ("conv_taps", c_int32),
+                ("norm_groups", c_int32), ("w_in", c_void_p), ("conv_w", c_void_p), ("conv_b", c_void_p),
+                ("dt_bias", c_void_p), ("a", c_void_p), ("d", c_void_p), ("out_norm_w", c_void_p), ("w_out", c_void_p)]
+
+
 class Layer(ctypes.Structure):
     _fields_ = [("mixer_kind", c_int32), ("ff_kind", c_int32), ("pre_mixer", Norm), ("post_mixer", Norm),
                 ("pre_ff", Norm), ("post_ff", Norm), ("attn", Attention), ("moe", Moe), ("shift", c_void_p),
                 ("latent", Latent), ("linear", Linear), ("dense", Dense), ("ssm", Ssm), ("delta", Delta),
-                ("mixer2_kind", c_int32), ("mixer_scale", c_float), ("mixer2_scale", c_float), ("parallel_ff", c_int32)]
+                ("mixer2_kind", c_int32), ("mixer_scale", c_float), ("mixer2_scale", c_float), ("parallel_ff", c_int32),
+                ("ssd", Ssd), ("mixer_out_norm", Norm), ("mixer2_out_norm", Norm)]
 
 
 class Desc(ctypes.Structure):
