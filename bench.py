@@ -89,7 +89,7 @@ def parse_args():
     ap.add_argument("--no-secondary", action="store_true", help="N>1: skip the fp32 Llama-2-7B line (configs[4])")
     ap.add_argument("--cpu-seconds", type=float, default=12.0, help="budget of the cpu_baseline leg")
     ap.add_argument("--seed", type=int, default=None)
-    ap.add_argument("--family", default=None, choices=["fobolorn", "kikunex", "vurazen"],
+    ap.add_argument("--family", default=None, choices=["fobolorn", "kikunex", "vurazen", "bukuvik"],
                     help="measure a batched model family (prefill and decode of the sequence-batch engine beside the "
                          "closest existing model at equal size) instead of the default workload")
     ap.add_argument("--family-sizes", default=None, help="comma-separated sizes of the family bench (s,m,debug)")

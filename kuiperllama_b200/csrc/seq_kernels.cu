@@ -1075,8 +1075,9 @@ int launch_qk_prepare(int dtype, const AttnShape& a, const RopeArgs& rope_, cons
   if (rope.dims < 0 || (rope.dims & 1) || rope.dims > a.dim || a.kv_heads % v_share_of(a) || a.heads % v_share_of(a) ||
       a.dim > 512)
     return KLLM_E_INVALID;
-  // a warp per head: few tokens get as many warps as there are query and key heads; a head's row lives in shared memory
-  int warps = T <= 64 ? std::min(32, std::max(4, a.heads + a.kv_heads)) : 4;
+  // a warp per head: few tokens get as many warps as there are query and key heads (at most 16: the kernel's registers
+  // do not fit 1024 threads); a head's row lives in shared memory
+  int warps = T <= 64 ? std::min(16, std::max(4, a.heads + a.kv_heads)) : 4;
   warps = std::max(1, std::min(warps, 48 * 1024 / (4 * a.dim)));
   const size_t smem = static_cast<size_t>(warps) * a.dim * sizeof(float);
   KLLM_SEQ_DISPATCH(dtype, (qk_prepare_kernel<AT><<<T, 32 * warps, smem, s>>>(a, rope, qkvg, qnorm_w, knorm_w, eps, tok_seq,

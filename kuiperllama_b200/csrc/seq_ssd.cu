@@ -9,8 +9,8 @@
 //
 // Everything here is fp32; only ssd_out's result (the input of the output projection) is in the compute type.
 //
-// State layout: [slots][heads][vdim][state] -- the `state` coordinates of one value column lie side by side, because the
-// lanes that share a column hold them interleaved (lane l: l, l + L, l + 2 L, ...).
+// State layout: [slots][heads][vdim][state] -- the `state` coordinates of one value column lie side by side; the lanes
+// that share a column hold contiguous runs of them.
 //
 // Long entries.  The recurrence is linear in S, so an entry is cut into segments of kSsdSeg rows that are walked at the
 // same time, each from an empty state (the first from the sequence's): with c_t the sum of a dt from the segment's start
@@ -32,7 +32,8 @@ namespace {
 
 constexpr unsigned kAll = 0xffffffffu;
 constexpr int kSsdThreads = 128;
-constexpr int kSsdRows = 16;          // state coordinates of a column per lane, at most
+constexpr int kSsdRows = 8;           // state coordinates of a column per lane (of each of 4 columns) ...
+constexpr int kSsdRowsWide = 16;      // ... or, for states beyond 256 coordinates, of each of 2 columns
 constexpr int kSsdSeg = 128;          // rows of a segment when long entries are walked in parallel
 constexpr int kSsdParallelFrom = 256; // entries longer than this are cut into segments
 
@@ -69,11 +70,45 @@ struct SsdScratch {
 };
 __host__ __device__ inline int ssd_segment_id(int first, int e, int seg) { return first / kSsdSeg + e + seg; }
 
-// One CTA: one entry (MODE 0) or one segment of an entry (MODE 1, 2), one head, COLS = kSsdThreads / L value columns.  L
-// lanes share a column; lane l keeps the state coordinates l, l + L, ... of its column in registers.  Chunks of rows are
-// staged in shared memory (B, C, the columns' x, dt and the decay), then walked one row after the other; only the read-out's
-// dot product is joined over the L lanes.
-template <int MODE>
+// Sums of CC accumulators over the L lanes that share a block of columns.  With L >= CC the lanes first trade halves
+// (a lane keeps the columns of its side and adds the partner's sums for them), so that CC values cost CC - 1 shuffles
+// instead of CC log2(CC); the remaining strides are plain butterflies.  Returns true in the lanes that hold a total;
+// `col` is then the column (0 .. CC - 1) of acc[0].  With L < CC lane 0 holds all CC totals (col = 0, acc[0 .. CC - 1]).
+template <int CC>
+__device__ __forceinline__ bool join_columns(float (&acc)[CC], int L, int lane, int* col, bool* all) {
+  *all = false, *col = 0;
+  if (L < CC) {
+    for (int o = 1; o < L; o <<= 1) {
+#pragma unroll
+      for (int c = 0; c < CC; ++c) acc[c] += __shfl_xor_sync(kAll, acc[c], o);
+    }
+    *all = true;
+    return lane == 0;
+  }
+  int stride = 1, at = 0;
+#pragma unroll
+  for (int half = CC / 2; half >= 1; half /= 2) {
+    const bool up = (lane & stride) != 0;
+#pragma unroll
+    for (int c = 0; c < half; ++c) {
+      const float keep = up ? acc[c + half] : acc[c];
+      const float send = up ? acc[c] : acc[c + half];
+      acc[c] = keep + __shfl_xor_sync(kAll, send, stride);
+    }
+    at += up ? half : 0;
+    stride <<= 1;
+  }
+  for (int o = stride; o < L; o <<= 1) acc[0] += __shfl_xor_sync(kAll, acc[0], o);
+  *col = at;
+  return lane < CC;
+}
+
+// One CTA: one entry (MODE 0) or one segment of an entry (MODE 1, 2), one head, COLS = blockDim.x / L * CC value columns.
+// L lanes share a block of CC columns; lane l keeps the state coordinates l RS .. l RS + RS - 1 of each of them in
+// registers (RS x CC values), so that a row's B and C are read once for CC columns and as 16-byte vectors.  Chunks of
+// rows are staged in shared memory (B and C padded with zeros to L RS coordinates, the columns' x, dt and the decay),
+// then walked one row after the other; only the read-out's dot products are joined over the L lanes.
+template <int MODE, int RS, int CC>
 __global__ void __launch_bounds__(kSsdThreads)
 ssd_scan_kernel(kllm_seq_ssd m, int L, int chunk, int segs_max, const float* __restrict__ proj, const float* __restrict__ xbc,
                 float* __restrict__ state, StepRows rows, const int32_t* __restrict__ ent_seq, float* __restrict__ y,
@@ -85,57 +120,59 @@ ssd_scan_kernel(kllm_seq_ssd m, int L, int chunk, int segs_max, const float* __r
   const int first = MODE == 0 ? e_first : e_first + seg * kSsdSeg;
   const int count = MODE == 0 ? e_count : min(kSsdSeg, e_count - seg * kSsdSeg);
   const int h = blockIdx.y, N = m.state, V = m.vdim, inner = ssd_inner(m);
-  const int COLS = kSsdThreads / L;
-  const int lane = threadIdx.x % L, col = threadIdx.x / L, pcol = blockIdx.x * COLS + col;
-  const bool live = pcol < V;
+  const int nthreads = blockDim.x, Ns = L * RS;  // Ns >= N: the padded row of B and C
+  const int COLS = nthreads / L * CC;
+  const int lane = threadIdx.x % L, cblock = threadIdx.x / L * CC, pcol0 = blockIdx.x * COLS + cblock;
   const int g = h / (m.heads / m.groups);
   const int C = ssd_conv_channels(m), P = ssd_proj_row(m);
   const int b_off = inner + g * N, c_off = inner + m.groups * N + g * N, dt_off = 2 * inner + 2 * m.groups * N + h;
   const float rate = m.a[h], skip = m.d[h], dt_bias = m.dt_bias[h];
 
-  extern __shared__ float sm[];
-  float* B_s = sm;                    // [chunk][N]
-  float* C_s = B_s + chunk * N;       // [chunk][N]
-  float* x_s = C_s + chunk * N;       // [chunk][COLS]
+  extern __shared__ __align__(16) float sm[];
+  float* B_s = sm;                    // [chunk][Ns]
+  float* C_s = B_s + chunk * Ns;      // [chunk][Ns]
+  float* x_s = C_s + chunk * Ns;      // [chunk][COLS]
   float* y_s = x_s + chunk * COLS;    // [chunk][COLS]
   float* dt_s = y_s + chunk * COLS;   // [chunk]
   float* dec_s = dt_s + chunk;        // [chunk]: exp(a dt)  (MODE 2: exp(c_t))
   float* cum_s = dec_s + chunk;       // [chunk]: c_t
 
-  float S[kSsdRows];
+  float S[CC][RS];
   const size_t sid = MODE == 0 ? 0 : ssd_segment_id(e_first, e, seg);
   {
-    const float* src = MODE == 2 ? sc.send + ((sid * m.heads + h) * V + (live ? pcol : 0)) * N
-                                 : state + ((static_cast<size_t>(seq) * m.heads + h) * V + (live ? pcol : 0)) * N;
+    const float* src = MODE == 2 ? sc.send + (sid * m.heads + h) * V * N : state + (static_cast<size_t>(seq) * m.heads + h) * V * N;
     const bool from_state = MODE == 2 || (pos0 > 0 && seg == 0);
 #pragma unroll
-    for (int k = 0; k < kSsdRows; ++k) {
-      const int n = lane + L * k;
-      S[k] = live && n < N && from_state ? src[n] : 0.f;
-    }
+    for (int c = 0; c < CC; ++c)
+#pragma unroll
+      for (int k = 0; k < RS; ++k) {
+        const int n = lane * RS + k;
+        S[c][k] = from_state && pcol0 + c < V && n < N ? src[static_cast<size_t>(pcol0 + c) * N + n] : 0.f;
+      }
   }
   float cum = 0.f;  // the sum of a dt since the segment's start (the same in every thread)
   for (int r0 = 0; r0 < count; r0 += chunk) {
     const int nr = min(chunk, count - r0);
     __syncthreads();
-    for (int i = threadIdx.x; i < nr * N; i += kSsdThreads) {
-      const size_t row = static_cast<size_t>(first + r0 + i / N) * C;
-      if (MODE != 2) B_s[i] = xbc[row + b_off + i % N];
-      C_s[i] = xbc[row + c_off + i % N];
+    for (int i = threadIdx.x; i < nr * Ns; i += nthreads) {
+      const int n = i % Ns;
+      const size_t row = static_cast<size_t>(first + r0 + i / Ns) * C;
+      if (MODE != 2) B_s[i] = n < N ? xbc[row + b_off + n] : 0.f;
+      C_s[i] = n < N ? xbc[row + c_off + n] : 0.f;
     }
     if (MODE != 2)
-      for (int i = threadIdx.x; i < nr * COLS; i += kSsdThreads) {
+      for (int i = threadIdx.x; i < nr * COLS; i += nthreads) {
         const int pc = blockIdx.x * COLS + i % COLS;
         x_s[i] = pc < V ? xbc[static_cast<size_t>(first + r0 + i / COLS) * C + h * V + pc] : 0.f;
       }
-    if (threadIdx.x < nr) {
-      const size_t row = static_cast<size_t>(first + r0 + threadIdx.x);
+    for (int i = threadIdx.x; i < nr; i += nthreads) {
+      const size_t row = static_cast<size_t>(first + r0 + i);
       if (MODE == 2) {
-        dec_s[threadIdx.x] = expf(sc.cum[row * m.heads + h]);
+        dec_s[i] = expf(sc.cum[row * m.heads + h]);
       } else {
         const float dt = softplusf(proj[row * P + dt_off] + dt_bias);
-        dt_s[threadIdx.x] = dt;
-        dec_s[threadIdx.x] = expf(rate * dt);
+        dt_s[i] = dt;
+        dec_s[i] = expf(rate * dt);
       }
     }
     __syncthreads();
@@ -145,51 +182,69 @@ ssd_scan_kernel(kllm_seq_ssd m, int L, int chunk, int segs_max, const float* __r
     }
     for (int r = 0; r < nr; ++r) {
       const float dec = dec_s[r];
-      const float* Bn = B_s + r * N;
-      const float* Cn = C_s + r * N;
-      float acc = 0.f;
+      float Cn[RS], acc[CC];
+#pragma unroll
+      for (int k = 0; k < RS; k += 4)
+        *reinterpret_cast<float4*>(Cn + k) = *reinterpret_cast<const float4*>(C_s + r * Ns + lane * RS + k);
       if (MODE == 2) {
 #pragma unroll
-        for (int k = 0; k < kSsdRows; ++k) {
-          const int n = lane + L * k;
-          if (n < N) acc = fmaf(S[k], Cn[n], acc);
+        for (int c = 0; c < CC; ++c) {
+          acc[c] = 0.f;
+#pragma unroll
+          for (int k = 0; k < RS; ++k) acc[c] = fmaf(S[c][k], Cn[k], acc[c]);
         }
       } else {
-        const float dx = dt_s[r] * x_s[r * COLS + col];
+        float Bn[RS], dx[CC];
 #pragma unroll
-        for (int k = 0; k < kSsdRows; ++k) {
-          const int n = lane + L * k;
-          if (n < N) {
-            S[k] = fmaf(dec, S[k], dx * Bn[n]);
-            acc = fmaf(S[k], Cn[n], acc);
+        for (int k = 0; k < RS; k += 4)
+          *reinterpret_cast<float4*>(Bn + k) = *reinterpret_cast<const float4*>(B_s + r * Ns + lane * RS + k);
+        const float dt = dt_s[r];
+#pragma unroll
+        for (int c = 0; c < CC; ++c) dx[c] = dt * x_s[r * COLS + cblock + c];
+#pragma unroll
+        for (int c = 0; c < CC; ++c) {
+          acc[c] = 0.f;
+#pragma unroll
+          for (int k = 0; k < RS; ++k) {
+            S[c][k] = fmaf(dec, S[c][k], dx[c] * Bn[k]);
+            acc[c] = fmaf(S[c][k], Cn[k], acc[c]);
           }
         }
       }
-      for (int o = L >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(kAll, acc, o);
-      if (lane == 0) y_s[r * COLS + col] = MODE == 2 ? dec * acc : fmaf(skip, x_s[r * COLS + col], acc);
+      int col;
+      bool all;
+      if (join_columns<CC>(acc, L, lane, &col, &all)) {
+        const int n_out = all ? CC : 1;
+        for (int c = 0; c < n_out; ++c) {
+          const int at = r * COLS + cblock + col + c;
+          y_s[at] = MODE == 2 ? dec * acc[c] : fmaf(skip, x_s[at], acc[c]);
+        }
+      }
     }
     if (MODE == 1)
       for (int r = 0; r < nr; ++r) cum = fmaf(rate, dt_s[r], cum);
     __syncthreads();
-    for (int i = threadIdx.x; i < nr * COLS; i += kSsdThreads) {
+    for (int i = threadIdx.x; i < nr * COLS; i += nthreads) {
       const int pc = blockIdx.x * COLS + i % COLS;
       if (pc >= V) continue;
       const size_t at = static_cast<size_t>(first + r0 + i / COLS) * inner + h * V + pc;
       if (MODE == 2) y[at] += y_s[i];
       else y[at] = y_s[i];
     }
-    if (MODE == 1 && blockIdx.x == 0 && threadIdx.x < nr)
-      sc.cum[static_cast<size_t>(first + r0 + threadIdx.x) * m.heads + h] = cum_s[threadIdx.x];
+    if (MODE == 1 && blockIdx.x == 0)
+      for (int i = threadIdx.x; i < nr; i += nthreads)
+        sc.cum[static_cast<size_t>(first + r0 + i) * m.heads + h] = cum_s[i];
   }
   if (MODE == 2) return;
-  float* dst = MODE == 1 ? sc.send + ((sid * m.heads + h) * V + (live ? pcol : 0)) * N
-                         : state + ((static_cast<size_t>(seq) * m.heads + h) * V + (live ? pcol : 0)) * N;
+  float* dst = MODE == 1 ? sc.send + (sid * m.heads + h) * V * N : state + (static_cast<size_t>(seq) * m.heads + h) * V * N;
   if (MODE == 1 && blockIdx.x == 0 && threadIdx.x == 0) sc.cend[sid * m.heads + h] = cum;
 #pragma unroll
-  for (int k = 0; k < kSsdRows; ++k) {
-    const int n = lane + L * k;
-    if (live && n < N) dst[n] = S[k];
-  }
+  for (int c = 0; c < CC; ++c)
+#pragma unroll
+    for (int k = 0; k < RS; ++k) {
+      const int n = lane * RS + k;
+      if (pcol0 + c < V && n < N) dst[static_cast<size_t>(pcol0 + c) * N + n] = S[c][k];
+    }
 }
 
 // One thread per (entry, head, value column, state coordinate): the start state of every segment after the first, and the
@@ -204,11 +259,22 @@ __global__ void ssd_carry_kernel(kllm_seq_ssd m, float* __restrict__ state, Step
   const int segs = (count + kSsdSeg - 1) / kSsdSeg;
   const int h = static_cast<int>(i / (static_cast<size_t>(m.vdim) * m.state));
   float carry = sc.send[ssd_segment_id(first, e, 0) * per + i];  // the first segment started from the sequence's state
-  for (int sg = 1; sg < segs; ++sg) {
-    const size_t sid = ssd_segment_id(first, e, sg);
-    const float own = sc.send[sid * per + i];
-    sc.send[sid * per + i] = carry;
-    carry = fmaf(expf(sc.cend[sid * m.heads + h]), carry, own);
+  constexpr int kAhead = 8;  // a batch of segments is loaded before the chain that depends on the one before it
+  for (int sg0 = 1; sg0 < segs; sg0 += kAhead) {
+    float own[kAhead], dec[kAhead];
+#pragma unroll
+    for (int j = 0; j < kAhead; ++j)
+      if (sg0 + j < segs) {
+        const size_t sid = ssd_segment_id(first, e, sg0 + j);
+        own[j] = sc.send[sid * per + i];
+        dec[j] = expf(sc.cend[sid * m.heads + h]);
+      }
+#pragma unroll
+    for (int j = 0; j < kAhead; ++j)
+      if (sg0 + j < segs) {
+        sc.send[ssd_segment_id(first, e, sg0 + j) * per + i] = carry;
+        carry = fmaf(dec[j], carry, own[j]);
+      }
   }
   state[static_cast<size_t>(ent_seq[e]) * per + i] = carry;
 }
@@ -243,11 +309,25 @@ inline int done() {
   return cuda_rc(cudaGetLastError());
 }
 
-// lanes that share a column: the smallest power of two that leaves each at most kSsdRows state coordinates
-inline int ssd_lanes(int state) {
+// lanes that share a block of columns: the smallest power of two that leaves each at most `per_lane` state coordinates
+inline int ssd_lanes(int state, int per_lane) {
   int L = 1;
-  while (L * kSsdRows < state) L *= 2;
+  while (L * per_lane < state) L *= 2;
   return L;
+}
+
+struct SsdLaunch {
+  dim3 grid;
+  int threads, L, chunk, segs_max;
+  size_t smem;
+};
+
+template <int MODE, int RS, int CC>
+void ssd_scan_launch(const SsdLaunch& l, const kllm_seq_ssd& m, const float* proj, const float* xbc, float* state,
+                     const StepRows& rows, const int32_t* ent_seq, float* y, const SsdScratch& sc, cudaStream_t s) {
+  ssd_scan_kernel<MODE, RS, CC><<<l.grid, l.threads, l.smem, s>>>(m, l.L, l.chunk, l.segs_max, proj, xbc, state, rows, ent_seq,
+                                                                 y, sc);
+  count_launch();
 }
 
 }  // namespace
@@ -269,39 +349,49 @@ size_t ssd_scan_scratch_bytes(const kllm_seq_ssd& m, int T, int n_entries, int m
 
 int launch_ssd_scan(const kllm_seq_ssd& m, const float* proj, const float* xbc, float* state, const StepRows& rows,
                     const int32_t* ent_seq, int max_count, int T, float* scratch, float* y, cudaStream_t s) {
-  if (m.state > 32 * kSsdRows || m.heads % m.groups) return KLLM_E_UNSUPPORTED;
-  const int L = ssd_lanes(m.state);
-  const int COLS = kSsdThreads / L;
+  if (m.state > 32 * kSsdRowsWide || m.heads % m.groups) return KLLM_E_UNSUPPORTED;
+  // a thread keeps 8 coordinates of 4 columns, or (states beyond 256) 16 coordinates of 2 columns
+  const bool wide = m.state > 32 * kSsdRows;
+  const int RS = wide ? kSsdRowsWide : kSsdRows, CC = wide ? 2 : 4;
+  SsdLaunch l;
+  l.L = ssd_lanes(m.state, RS);
+  // as many threads as the head's columns need, in whole warps
+  const int col_blocks = (m.vdim + CC - 1) / CC;
+  l.threads = std::min(kSsdThreads, (l.L * col_blocks + 31) / 32 * 32);
+  const int COLS = l.threads / l.L * CC;
   const bool segments = max_count > kSsdParallelFrom && scratch != nullptr;
   const int longest = segments ? kSsdSeg : max_count;
   auto smem_for = [&](int chunk) {
-    return static_cast<size_t>(chunk) * (2 * m.state + 2 * COLS + 3) * sizeof(float);
+    return static_cast<size_t>(chunk) * (2 * l.L * RS + 2 * COLS + 3) * sizeof(float);
   };
   int chunk = 32;
   while (chunk > 1 && (smem_for(chunk) > 48 * 1024 || chunk / 2 >= longest)) chunk /= 2;
   if (smem_for(chunk) > 48 * 1024) return KLLM_E_UNSUPPORTED;
+  l.chunk = chunk, l.smem = smem_for(chunk);
   const unsigned blocks = (m.vdim + COLS - 1) / COLS;
+#define KLLM_SSD_SCAN(MODE, sc)                                                                                    \
+  (wide ? ssd_scan_launch<MODE, kSsdRowsWide, 2>(l, m, proj, xbc, state, rows, ent_seq, y, sc, s)                  \
+        : ssd_scan_launch<MODE, kSsdRows, 4>(l, m, proj, xbc, state, rows, ent_seq, y, sc, s))
   if (!segments) {
-    const dim3 grid(blocks, m.heads, rows.n_entries);
-    ssd_scan_kernel<0><<<grid, kSsdThreads, smem_for(chunk), s>>>(m, L, chunk, 1, proj, xbc, state, rows, ent_seq, y,
-                                                                 SsdScratch{});
-    return done();
+    l.grid = dim3(blocks, m.heads, rows.n_entries), l.segs_max = 1;
+    KLLM_SSD_SCAN(0, SsdScratch{});
+    return cuda_rc(cudaGetLastError());
   }
   const size_t segs = static_cast<size_t>(T) / kSsdSeg + rows.n_entries + 1;
   SsdScratch sc;
   sc.cum = scratch;
   sc.send = sc.cum + static_cast<size_t>(T) * m.heads;
   sc.cend = sc.send + segs * m.heads * m.vdim * m.state;
-  const int segs_max = (max_count + kSsdSeg - 1) / kSsdSeg;
-  const dim3 grid(blocks, m.heads, rows.n_entries * segs_max);
-  ssd_scan_kernel<1><<<grid, kSsdThreads, smem_for(chunk), s>>>(m, L, chunk, segs_max, proj, xbc, state, rows, ent_seq, y, sc);
-  count_launch();
+  l.segs_max = (max_count + kSsdSeg - 1) / kSsdSeg;
+  l.grid = dim3(blocks, m.heads, rows.n_entries * l.segs_max);
+  KLLM_SSD_SCAN(1, sc);
   const size_t per = static_cast<size_t>(m.heads) * m.vdim * m.state;
   const dim3 cgrid(static_cast<unsigned>((per + 127) / 128), rows.n_entries);
   ssd_carry_kernel<<<cgrid, 128, 0, s>>>(m, state, rows, ent_seq, sc);
   count_launch();
-  ssd_scan_kernel<2><<<grid, kSsdThreads, smem_for(chunk), s>>>(m, L, chunk, segs_max, proj, xbc, state, rows, ent_seq, y, sc);
-  return done();
+  KLLM_SSD_SCAN(2, sc);
+#undef KLLM_SSD_SCAN
+  return cuda_rc(cudaGetLastError());
 }
 
 int launch_ssd_out(int dtype, const kllm_seq_ssd& m, const float* y, const float* proj, float eps, void* out, int T,

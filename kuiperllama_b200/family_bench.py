@@ -1,7 +1,7 @@
-"""`bench.py --family fobolorn | kikunex | vurazen`: prefill and decode throughput of a batched family (sequence-batch
+"""`bench.py --family fobolorn | kikunex | vurazen | bukuvik`: prefill and decode throughput of a batched family (sequence-batch
 engine) at sizes that resemble a real model's layers, random weights, beside the closest existing model at equal width,
 heads, active feed-forward size and number of layer runs: Fobolorn beside the Llama family of the single-sequence decoder,
-Kikunex beside Fobolorn, Vurazen beside Kikunex.
+Kikunex beside Fobolorn, Vurazen beside Kikunex, Bukuvik beside Vurazen.
 
 What is timed.  A step is the call a server makes: kllm_seq_step() with token ids in host memory and the greedy ids
 read back to host memory, blocking -- so every number here is end to end.  Between timed steps a buffer larger than
@@ -19,7 +19,7 @@ import statistics
 import time
 from pathlib import Path
 
-from .sequence import BF16, F32, FobolornShape, KikunexShape, SeqEngine, VurazenShape, load_seq_library
+from .sequence import BF16, BukuvikShape, F32, FobolornShape, KikunexShape, SeqEngine, VurazenShape, load_seq_library
 
 ROOT = Path(__file__).resolve().parent.parent
 
@@ -54,6 +54,56 @@ VURAZEN_SIZES = {
     "debug": VurazenShape("vurazen-debug", 256, 4096, _VP[:3], (1, 3, 2), 512, 8, 16, 4, 32, 32, 4, 2, 32, 96, 2, 16,
                           4, 2, 32, 32, 16, 512, 8, 2, 128, 256),
 }
+
+
+def _bp(ff):
+    return (("parallel", ff), ("attention", ff), ("attention", ff), ("parallel", ff), ("parallel", ff), ("attention", ff))
+
+
+BUKUVIK_SIZES = {
+    # the sizes of VURAZEN_SIZES: same width, head counts and number of layer runs (six layers, none looped); differential
+    # attention with 16 heads of 2 x 64 (values 128) over 4 key heads and a window of 1024; in the pair a unit-normed
+    # attention with the window of Vurazen's (512, 4 kept tokens) beside a duality mixer as wide as Vurazen's scan
+    # (inner = 2 x width) with heads of 64 and 128 states; dense feed-forwards of 4 x width
+    "s": BukuvikShape("bukuvik-s", 1024, 32000, _bp(4096), 16, 4, 64, 128, 1024, 32, 16, 4, 64, 64, 512, 4, 32,
+                      32, 64, 128, 2, 2),
+    "m": BukuvikShape("bukuvik-m", 2048, 32000, _bp(8192), 16, 4, 128, 128, 1024, 64, 16, 4, 128, 128, 512, 4, 64,
+                      64, 64, 128, 2, 2),
+    "debug": BukuvikShape("bukuvik-debug", 256, 4096, _bp(512)[:3], 4, 2, 32, 64, 96, 16, 4, 2, 32, 32, 64, 2, 16,
+                          8, 32, 16, 2, 2),
+}
+
+
+def bukuvik_costs(shape, prompt_len):
+    """FLOPs of a prompt step by phase class of the engine's profile."""
+    W, T = shape.width, prompt_len
+    n_att = sum(1 for m, _ in shape.pattern if m == "attention")
+    n_par = shape.layers - n_att
+
+    def pairs(window, keep):
+        win = min(window, T)
+        return T * win - win * (win - 1) / 2 + max(0, T - win) * keep
+    # two maps per head, each with its own scores and its own weighted sum of the values
+    attn_diff = 2 * pairs(shape.window, 0) * 2 * shape.heads * (shape.dim + shape.vdim)
+    attn_left = 2 * pairs(shape.l_window, shape.l_keep_first) * shape.l_heads * (shape.l_dim + shape.l_vdim)
+    # per token, head and state element: decay, update, read-out (multiply-adds)
+    attn_right = T * shape.s_heads * 6 * shape.s_vdim * shape.s_state
+    return {"in_proj": 2 * T * W * (n_att * shape.n_in("attention") + n_par * (shape.n_in("left") + shape.n_in("right"))),
+            "attention": n_att * attn_diff + n_par * (attn_left + attn_right),
+            "out_proj": 2 * T * W * (n_att * shape.n_out("attention") + n_par * (shape.n_out("left") + shape.n_out("right"))),
+            "experts": 2 * T * sum(2 * (f or 0) * W for _, f in shape.pattern),
+            "head": 2 * shape.vocab * W}
+
+
+def bukuvik_decode_bytes(shape, B, ctx, es):
+    """Bytes a decode step must move, by phase class: weights once per step, the windows' keys and values, the states."""
+    W = shape.width
+    n_att = sum(1 for m, _ in shape.pattern if m == "attention")
+    n_par = shape.layers - n_att
+    return {"in_proj": (n_att * shape.n_in("attention") + n_par * (shape.n_in("left") + shape.n_in("right"))) * W * es,
+            "out_proj": (n_att * shape.n_out("attention") + n_par * (shape.n_out("left") + shape.n_out("right"))) * W * es,
+            "experts": sum(2 * (f or 0) * W for _, f in shape.pattern) * es,
+            "attention": shape.state_bytes_per_step(B, ctx, es), "head": shape.vocab * W * es}
 
 
 def vurazen_costs(shape, prompt_len):
@@ -201,7 +251,9 @@ def bench_engine(torch, shape, dtype, prompt_len, ctx, batches, steps, warm, flu
     sec = statistics.median(times)
     kiku = isinstance(shape, KikunexShape)
     vura = isinstance(shape, VurazenShape)
-    phase_flops = (vurazen_costs if vura else kikunex_costs if kiku else fobolorn_costs)(shape, prompt_len)
+    buku = isinstance(shape, BukuvikShape)
+    phase_flops = (bukuvik_costs if buku else vurazen_costs if vura else kikunex_costs if kiku else
+                   fobolorn_costs)(shape, prompt_len)
     flops = sum(phase_flops.values())
     out["prefill"] = {"tokens": prompt_len, "tok_s": prompt_len / sec, "ms": sec * 1e3, "launches": launches,
                       "tflops": flops / sec / 1e12, "frac_of_bf16_peak": flops / sec / 1e12 / tf if dtype == BF16 else None,
@@ -231,8 +283,8 @@ def bench_engine(torch, shape, dtype, prompt_len, ctx, batches, steps, warm, flu
         # bytes a step must read: the active weights (distinct experts per token, an upper bound when tokens share
         # experts) and the cached keys / values
         W = shape.width
-        if vura:
-            phase_bytes = vurazen_decode_bytes(shape, B, ctx, es)
+        if vura or buku:
+            phase_bytes = (bukuvik_decode_bytes if buku else vurazen_decode_bytes)(shape, B, ctx, es)
             bytes_step = shape.weight_elems_per_step(B) * es + phase_bytes["attention"]
             out["decode"][str(B)] = {
                 "batch": B, "context": ctx, "tok_s": B / sec, "ms_per_step": sec * 1e3, "launches": launches,
@@ -381,6 +433,8 @@ def run(args, emit):
         return run_kikunex(args, emit, torch, sizes, steps, warm, flush, hbm, tf, src)
     if args.family == "vurazen":
         return run_vurazen(args, emit, torch, sizes, steps, warm, flush, hbm, tf, src)
+    if args.family == "bukuvik":
+        return run_bukuvik(args, emit, torch, sizes, steps, warm, flush, hbm, tf, src)
     line = {"family": "fobolorn", "metric": "prefill_and_decode_tokens_per_s", "n_gpus": 1, "steps": steps, "warmup": warm,
             "data": "synthetic", "peaks": {"hbm_gbs": hbm, "bf16_tflops": tf, "source": src},
             "config": {"l2": "a 256 MiB buffer is written between timed steps", "timing": "wall clock around the blocking "
@@ -433,6 +487,27 @@ def run_vurazen(args, emit, torch, sizes, steps, warm, flush, hbm, tf, src):
         entry = {"shape": {k: v for k, v in shape.__dict__.items()} | {"runs": shape.runs}, "vurazen": [], "closest": []}
         for dtype in (BF16, F32):
             entry["vurazen"].append(bench_engine(torch, shape, dtype, prompt, ctx, [1, 8], steps, warm, flush, hbm, tf))
+            entry["closest"].append(bench_engine(torch, close, dtype, prompt, ctx, [1, 8], steps, warm, flush, hbm, tf))
+        entry["closest_model"] = close.name
+        line["sizes"][name] = entry
+    emit(line)
+
+
+def run_bukuvik(args, emit, torch, sizes, steps, warm, flush, hbm, tf, src):
+    """Bukuvik beside its closest existing model, Vurazen (the same engine: a windowed softmax attention that keeps the
+    first tokens beside a recurrent mixer with a short convolution in one layer, a scan with input-dependent decays), at
+    equal width, head counts and layer runs: whole steps end to end, and the engine's phase classes side by side."""
+    line = {"family": "bukuvik", "metric": "prefill_and_decode_tokens_per_s", "n_gpus": 1, "steps": steps, "warmup": warm,
+            "data": "synthetic", "peaks": {"hbm_gbs": hbm, "bf16_tflops": tf, "source": src},
+            "config": {"l2": "a 256 MiB buffer is written between timed steps", "timing": "wall clock around the blocking "
+                       "step call (token ids from host memory, greedy ids back to host memory); phases by CUDA events"},
+            "sizes": {}}
+    for name in sizes:
+        shape, close = BUKUVIK_SIZES[name], VURAZEN_SIZES[name]
+        ctx, prompt = (256, 512) if name == "debug" else (1024, 2048)
+        entry = {"shape": {k: v for k, v in shape.__dict__.items()} | {"runs": shape.runs}, "bukuvik": [], "closest": []}
+        for dtype in (BF16, F32):
+            entry["bukuvik"].append(bench_engine(torch, shape, dtype, prompt, ctx, [1, 8], steps, warm, flush, hbm, tf))
             entry["closest"].append(bench_engine(torch, close, dtype, prompt, ctx, [1, 8], steps, warm, flush, hbm, tf))
         entry["closest_model"] = close.name
         line["sizes"][name] = entry

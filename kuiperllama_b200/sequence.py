@@ -2,7 +2,7 @@
 device memory, the engine and every kernel are the product library's.  Like the rest of this package it has no
 fallback: without libkllm_seq.so (or libkllm_b200.so, which carries the same symbols) it raises.
 
-`FobolornShape` / `KikunexShape` / `VurazenShape` + `SeqEngine` build a random-weight model of a family directly in device memory
+`FobolornShape` / `KikunexShape` / `VurazenShape` / `BukuvikShape` + `SeqEngine` build a random-weight model of a family directly in device memory
 (no model folder), for measurements at sizes that resemble a real model's layers.
 """
 from __future__ import annotations
@@ -350,8 +350,81 @@ class VurazenShape:
         return total
 
 
+@dataclass
+class BukuvikShape:
+    """A Bukuvik model: `pattern` lists the layers ("attention" | "parallel", feed-forward size or None)."""
+    name: str
+    width: int
+    vocab: int
+    pattern: tuple
+    heads: int           # differential attention
+    kv_heads: int
+    dim: int
+    vdim: int
+    window: int
+    rot_dims: int
+    l_heads: int         # the pair's attention (unit-normed, rescaled rotation, kept first tokens)
+    l_kv_heads: int
+    l_dim: int
+    l_vdim: int
+    l_window: int
+    l_keep_first: int
+    l_rot_dims: int
+    s_heads: int         # the pair's duality mixer
+    s_vdim: int
+    s_state: int
+    s_groups: int
+    s_norm_groups: int
+    taps: int = 4
+    softcap: float = 50.0
+    diff: float = 0.3
+    eps: float = 1e-5
+
+    @property
+    def layers(self):
+        return len(self.pattern)
+
+    @property
+    def runs(self):
+        return len(self.pattern)
+
+    def run_order(self):
+        return [(i, -1, 0) for i in range(self.layers)]
+
+    def n_in(self, kind):
+        if kind == "attention":
+            return 2 * (self.heads + self.kv_heads) * self.dim + (self.kv_heads + self.heads) * self.vdim
+        if kind == "left":
+            return (self.l_heads + self.l_kv_heads) * self.l_dim + (self.l_kv_heads + self.l_heads) * self.l_vdim
+        return 2 * self.s_heads * self.s_vdim + 2 * self.s_groups * self.s_state + self.s_heads
+
+    def n_out(self, kind):
+        return {"attention": self.heads * self.vdim, "left": self.l_heads * self.l_vdim, "right": self.s_heads * self.s_vdim}[kind]
+
+    def mixer_weight_elems(self, kind):
+        parts = ("attention",) if kind == "attention" else ("left", "right")
+        return sum((self.n_in(k) + self.n_out(k)) * self.width for k in parts)
+
+    def weight_elems_per_step(self, batch):
+        return self.vocab * self.width + sum(self.mixer_weight_elems(m) + 2 * (f or 0) * self.width for m, f in self.pattern)
+
+    def flops_per_token(self):
+        return 2 * self.weight_elems_per_step(1)
+
+    def state_bytes_per_step(self, batch, ctx, es):
+        """Cache and state a decode step touches: the windows' keys and values, the duality state (read and written)."""
+        total = 0
+        for m, _ in self.pattern:
+            if m == "attention":
+                total += batch * min(ctx, self.window) * self.kv_heads * (2 * self.dim + self.vdim) * es
+            else:
+                total += batch * min(ctx, self.l_window + self.l_keep_first) * self.l_kv_heads * (self.l_dim + self.l_vdim) * es
+                total += batch * 2 * self.s_heads * self.s_vdim * self.s_state * 4
+        return total
+
+
 class SeqEngine:
-    """A random-weight model (Fobolorn, Kikunex or Vurazen, by the shape's class) in device memory behind the engine's C-ABI."""
+    """A random-weight model (Fobolorn, Kikunex, Vurazen or Bukuvik, by the shape's class) in device memory behind the engine's C-ABI."""
 
     def __init__(self, shape, dtype=BF16, max_tokens=4096, max_seqs=16, page=0, seed=1):
         import torch
@@ -363,6 +436,9 @@ class SeqEngine:
             return
         if isinstance(shape, VurazenShape):
             self._init_vurazen(shape, dtype, max_tokens, max_seqs, page, seed)
+            return
+        if isinstance(shape, BukuvikShape):
+            self._init_bukuvik(shape, dtype, max_tokens, max_seqs, page, seed)
             return
         td = torch.bfloat16 if dtype == BF16 else torch.float32
         g = torch.Generator(device="cuda").manual_seed(seed)
@@ -616,6 +692,101 @@ class SeqEngine:
         d.final_norm = norm()
         d.head = rnd(shape.vocab, W, std=W ** -0.5).data_ptr()
         d.embed_scale, d.logit_softcap = 1.0, 30.0
+        d.max_tokens, d.max_seqs, d.page_tokens = max_tokens, max_seqs, page
+        self._desc = (d, layers, run_layer, run_add, run_embed)
+        self.handle = c_void_p()
+        torch.cuda.synchronize()
+        _check(self.lib, self.lib.kllm_seq_create(ctypes.byref(d), None, ctypes.byref(self.handle)), "kllm_seq_create")
+
+    def _init_bukuvik(self, shape, dtype, max_tokens, max_seqs, page, seed):
+        torch = self.torch
+        td = torch.bfloat16 if dtype == BF16 else torch.float32
+        g = torch.Generator(device="cuda").manual_seed(seed)
+        keep = self._keep = []
+        W = shape.width
+
+        def rnd(*dims, std, t=td, mean=0.0):
+            x = (torch.randn(*dims, device="cuda", generator=g) * std + mean).to(t).contiguous()
+            keep.append(x)
+            return x
+
+        def f32(*dims, std, mean=0.0):
+            return rnd(*dims, std=std, t=torch.float32, mean=mean)
+
+        def out_norm(scale=1.0):
+            return Norm(f32(W, std=0.05 * scale, mean=scale).data_ptr(), None, 1)
+
+        def frequencies(dims, base, factor=None):
+            f = torch.tensor([base ** (-2.0 * i / dims) for i in range(dims // 2)], device="cuda")
+            if factor:  # the slow half of the waves is stretched
+                f[dims // 4:] /= factor
+            keep.append(f)
+            return f.data_ptr()
+
+        def attention(a, heads, kv_heads, dim, vdim, window, rot_dims, n_in):
+            a.heads, a.kv_heads, a.dim, a.vdim, a.scale, a.window = heads, kv_heads, dim, vdim, dim ** -0.5, window
+            a.gate, a.rope_dims, a.rope_base, a.rope_pairing = 2, rot_dims, 1e4, 0
+            a.w_in = rnd(n_in, W, std=W ** -0.5).data_ptr()
+            a.w_out = rnd(W, heads * vdim, std=(heads * vdim) ** -0.5).data_ptr()
+
+        layers = (Layer * shape.layers)()
+        for L, (mix, ff) in zip(layers, shape.pattern):
+            L.pre_mixer, L.pre_ff = Norm(None, None, 2), Norm(None, None, 2)
+            L.post_mixer = out_norm(0.7)
+            L.mixer_scale = L.mixer2_scale = 1.0
+            if mix == "attention":
+                L.mixer_kind = 1
+                a = L.attn
+                attention(a, shape.heads, shape.kv_heads, shape.dim, shape.vdim, shape.window, shape.rot_dims,
+                          shape.n_in("attention"))
+                a.qk_norm, a.softcap, a.differential = 1, shape.softcap, 1
+                a.q_norm_w = f32(shape.dim, std=0.05, mean=1.0).data_ptr()
+                a.k_norm_w = f32(shape.dim, std=0.05, mean=1.0).data_ptr()
+                a.rope_freq, a.rope_mag = frequencies(shape.rot_dims, 2.5e5), 1.0
+                a.diff_lambda, a.diff_out_scale = 0.8, 1.0 - shape.diff
+            else:
+                L.mixer_kind, L.mixer2_kind = 1, 6
+                L.mixer_scale = L.mixer2_scale = 0.5
+                L.mixer_out_norm, L.mixer2_out_norm = out_norm(), out_norm()
+                a = L.attn
+                attention(a, shape.l_heads, shape.l_kv_heads, shape.l_dim, shape.l_vdim, shape.l_window, shape.l_rot_dims,
+                          shape.n_in("left"))
+                a.qk_norm, a.keep_first = 2, shape.l_keep_first
+                a.scale = 2.0 * shape.l_dim ** -0.5
+                a.rope_freq, a.rope_mag = frequencies(shape.l_rot_dims, 5e5, 8.0), 0.1 * math.log(8.0) + 1.0
+                b = L.ssd
+                b.heads, b.vdim, b.state, b.groups = shape.s_heads, shape.s_vdim, shape.s_state, shape.s_groups
+                b.conv_taps, b.norm_groups = shape.taps, shape.s_norm_groups
+                inner, ch = shape.s_heads * shape.s_vdim, shape.s_heads * shape.s_vdim + 2 * shape.s_groups * shape.s_state
+                b.w_in = rnd(shape.n_in("right"), W, std=W ** -0.5).data_ptr()
+                b.conv_w = f32(ch, shape.taps, std=0.5).data_ptr()
+                b.conv_b = f32(ch, std=0.1).data_ptr()
+                b.dt_bias = f32(shape.s_heads, std=0.5, mean=-2.0).data_ptr()
+                rates = -torch.rand(shape.s_heads, device="cuda", generator=g) * 4.0 - 0.05
+                keep.append(rates)
+                b.a = rates.data_ptr()
+                b.d = f32(shape.s_heads, std=1.0).data_ptr()
+                b.out_norm_w = f32(inner, std=0.05, mean=1.0).data_ptr()
+                b.w_out = rnd(W, inner, std=inner ** -0.5).data_ptr()
+            L.ff_kind = 2 if ff else 0
+            if ff:
+                L.post_ff = out_norm(0.7)
+                d = L.dense
+                d.ff, d.act = ff, 1
+                d.up = rnd(ff, W, std=W ** -0.5).data_ptr()
+                d.down = rnd(W, ff, std=ff ** -0.5).data_ptr()
+        order = shape.run_order()
+        run_layer = (c_int32 * len(order))(*[i for i, _, _ in order])
+        run_add = (c_int32 * len(order))(*[p for _, p, _ in order])
+        run_embed = (c_int32 * len(order))(*[x for _, _, x in order])
+        d = Desc()
+        d.dtype, d.width, d.vocab, d.norm_eps = dtype, W, shape.vocab, shape.eps
+        d.n_layers, d.layers = shape.layers, layers
+        d.n_runs, d.run_layer, d.run_add, d.run_embed = len(order), run_layer, run_add, run_embed
+        d.embed = rnd(shape.vocab, W, std=1.0).data_ptr()
+        d.final_norm = out_norm()
+        d.head = d.embed  # the classifier is the embedding table
+        d.embed_scale = W ** 0.5
         d.max_tokens, d.max_seqs, d.page_tokens = max_tokens, max_seqs, page
         self._desc = (d, layers, run_layer, run_add, run_embed)
         self.handle = c_void_p()
