@@ -17,7 +17,7 @@
 // to row t, the true output is y_t = y'_t + exp(c_t) S_start^T C_t, y' the segment's own walk.
 //   ssd_scan_kernel<1>   the segment's own walk: y', c_t of every row, the segment's last S' and c
 //   ssd_carry_kernel     S_start of every segment, one after the other; the sequence's new state
-//   ssd_scan_kernel<2>   y += exp(c_t) S_start^T C_t
+//   ssd_finish_kernel    y += exp(c_t) S_start^T C_t: per segment and head a product [rows x state] [state x vdim]
 #include <cuda_runtime.h>
 
 #include <algorithm>
@@ -103,7 +103,7 @@ __device__ __forceinline__ bool join_columns(float (&acc)[CC], int L, int lane, 
   return lane < CC;
 }
 
-// One CTA: one entry (MODE 0) or one segment of an entry (MODE 1, 2), one head, COLS = blockDim.x / L * CC value columns.
+// One CTA: one entry (MODE 0) or one segment of an entry (MODE 1), one head, COLS = blockDim.x / L * CC value columns.
 // L lanes share a block of CC columns; lane l keeps the state coordinates l RS .. l RS + RS - 1 of each of them in
 // registers (RS x CC values), so that a row's B and C are read once for CC columns and as 16-byte vectors.  Chunks of
 // rows are staged in shared memory (B and C padded with zeros to L RS coordinates, the columns' x, dt and the decay),
@@ -116,7 +116,6 @@ ssd_scan_kernel(kllm_seq_ssd m, int L, int chunk, int segs_max, const float* __r
   const int e = MODE == 0 ? blockIdx.z : blockIdx.z / segs_max, seg = MODE == 0 ? 0 : blockIdx.z % segs_max;
   const int e_first = rows.ent_first[e], e_count = rows.ent_count[e], pos0 = rows.ent_pos0[e], seq = ent_seq[e];
   if (MODE != 0 && seg * kSsdSeg >= e_count) return;
-  if (MODE == 2 && seg == 0) return;  // the first segment started from the true state
   const int first = MODE == 0 ? e_first : e_first + seg * kSsdSeg;
   const int count = MODE == 0 ? e_count : min(kSsdSeg, e_count - seg * kSsdSeg);
   const int h = blockIdx.y, N = m.state, V = m.vdim, inner = ssd_inner(m);
@@ -134,14 +133,14 @@ ssd_scan_kernel(kllm_seq_ssd m, int L, int chunk, int segs_max, const float* __r
   float* x_s = C_s + chunk * Ns;      // [chunk][COLS]
   float* y_s = x_s + chunk * COLS;    // [chunk][COLS]
   float* dt_s = y_s + chunk * COLS;   // [chunk]
-  float* dec_s = dt_s + chunk;        // [chunk]: exp(a dt)  (MODE 2: exp(c_t))
+  float* dec_s = dt_s + chunk;        // [chunk]: exp(a dt)
   float* cum_s = dec_s + chunk;       // [chunk]: c_t
 
   float S[CC][RS];
   const size_t sid = MODE == 0 ? 0 : ssd_segment_id(e_first, e, seg);
   {
-    const float* src = MODE == 2 ? sc.send + (sid * m.heads + h) * V * N : state + (static_cast<size_t>(seq) * m.heads + h) * V * N;
-    const bool from_state = MODE == 2 || (pos0 > 0 && seg == 0);
+    const float* src = state + (static_cast<size_t>(seq) * m.heads + h) * V * N;
+    const bool from_state = pos0 > 0 && seg == 0;
 #pragma unroll
     for (int c = 0; c < CC; ++c)
 #pragma unroll
@@ -157,23 +156,17 @@ ssd_scan_kernel(kllm_seq_ssd m, int L, int chunk, int segs_max, const float* __r
     for (int i = threadIdx.x; i < nr * Ns; i += nthreads) {
       const int n = i % Ns;
       const size_t row = static_cast<size_t>(first + r0 + i / Ns) * C;
-      if (MODE != 2) B_s[i] = n < N ? xbc[row + b_off + n] : 0.f;
+      B_s[i] = n < N ? xbc[row + b_off + n] : 0.f;
       C_s[i] = n < N ? xbc[row + c_off + n] : 0.f;
     }
-    if (MODE != 2)
-      for (int i = threadIdx.x; i < nr * COLS; i += nthreads) {
-        const int pc = blockIdx.x * COLS + i % COLS;
-        x_s[i] = pc < V ? xbc[static_cast<size_t>(first + r0 + i / COLS) * C + h * V + pc] : 0.f;
-      }
+    for (int i = threadIdx.x; i < nr * COLS; i += nthreads) {
+      const int pc = blockIdx.x * COLS + i % COLS;
+      x_s[i] = pc < V ? xbc[static_cast<size_t>(first + r0 + i / COLS) * C + h * V + pc] : 0.f;
+    }
     for (int i = threadIdx.x; i < nr; i += nthreads) {
-      const size_t row = static_cast<size_t>(first + r0 + i);
-      if (MODE == 2) {
-        dec_s[i] = expf(sc.cum[row * m.heads + h]);
-      } else {
-        const float dt = softplusf(proj[row * P + dt_off] + dt_bias);
-        dt_s[i] = dt;
-        dec_s[i] = expf(rate * dt);
-      }
+      const float dt = softplusf(proj[static_cast<size_t>(first + r0 + i) * P + dt_off] + dt_bias);
+      dt_s[i] = dt;
+      dec_s[i] = expf(rate * dt);
     }
     __syncthreads();
     if (MODE == 1 && threadIdx.x == 0) {
@@ -182,33 +175,22 @@ ssd_scan_kernel(kllm_seq_ssd m, int L, int chunk, int segs_max, const float* __r
     }
     for (int r = 0; r < nr; ++r) {
       const float dec = dec_s[r];
-      float Cn[RS], acc[CC];
+      float Bn[RS], Cn[RS], dx[CC], acc[CC];
 #pragma unroll
-      for (int k = 0; k < RS; k += 4)
+      for (int k = 0; k < RS; k += 4) {
+        *reinterpret_cast<float4*>(Bn + k) = *reinterpret_cast<const float4*>(B_s + r * Ns + lane * RS + k);
         *reinterpret_cast<float4*>(Cn + k) = *reinterpret_cast<const float4*>(C_s + r * Ns + lane * RS + k);
-      if (MODE == 2) {
+      }
+      const float dt = dt_s[r];
 #pragma unroll
-        for (int c = 0; c < CC; ++c) {
-          acc[c] = 0.f;
+      for (int c = 0; c < CC; ++c) dx[c] = dt * x_s[r * COLS + cblock + c];
 #pragma unroll
-          for (int k = 0; k < RS; ++k) acc[c] = fmaf(S[c][k], Cn[k], acc[c]);
-        }
-      } else {
-        float Bn[RS], dx[CC];
+      for (int c = 0; c < CC; ++c) {
+        acc[c] = 0.f;
 #pragma unroll
-        for (int k = 0; k < RS; k += 4)
-          *reinterpret_cast<float4*>(Bn + k) = *reinterpret_cast<const float4*>(B_s + r * Ns + lane * RS + k);
-        const float dt = dt_s[r];
-#pragma unroll
-        for (int c = 0; c < CC; ++c) dx[c] = dt * x_s[r * COLS + cblock + c];
-#pragma unroll
-        for (int c = 0; c < CC; ++c) {
-          acc[c] = 0.f;
-#pragma unroll
-          for (int k = 0; k < RS; ++k) {
-            S[c][k] = fmaf(dec, S[c][k], dx[c] * Bn[k]);
-            acc[c] = fmaf(S[c][k], Cn[k], acc[c]);
-          }
+        for (int k = 0; k < RS; ++k) {
+          S[c][k] = fmaf(dec, S[c][k], dx[c] * Bn[k]);
+          acc[c] = fmaf(S[c][k], Cn[k], acc[c]);
         }
       }
       int col;
@@ -217,7 +199,7 @@ ssd_scan_kernel(kllm_seq_ssd m, int L, int chunk, int segs_max, const float* __r
         const int n_out = all ? CC : 1;
         for (int c = 0; c < n_out; ++c) {
           const int at = r * COLS + cblock + col + c;
-          y_s[at] = MODE == 2 ? dec * acc[c] : fmaf(skip, x_s[at], acc[c]);
+          y_s[at] = fmaf(skip, x_s[at], acc[c]);
         }
       }
     }
@@ -228,14 +210,12 @@ ssd_scan_kernel(kllm_seq_ssd m, int L, int chunk, int segs_max, const float* __r
       const int pc = blockIdx.x * COLS + i % COLS;
       if (pc >= V) continue;
       const size_t at = static_cast<size_t>(first + r0 + i / COLS) * inner + h * V + pc;
-      if (MODE == 2) y[at] += y_s[i];
-      else y[at] = y_s[i];
+      y[at] = y_s[i];
     }
     if (MODE == 1 && blockIdx.x == 0)
       for (int i = threadIdx.x; i < nr; i += nthreads)
         sc.cum[static_cast<size_t>(first + r0 + i) * m.heads + h] = cum_s[i];
   }
-  if (MODE == 2) return;
   float* dst = MODE == 1 ? sc.send + (sid * m.heads + h) * V * N : state + (static_cast<size_t>(seq) * m.heads + h) * V * N;
   if (MODE == 1 && blockIdx.x == 0 && threadIdx.x == 0) sc.cend[sid * m.heads + h] = cum;
 #pragma unroll
@@ -245,6 +225,66 @@ ssd_scan_kernel(kllm_seq_ssd m, int L, int chunk, int segs_max, const float* __r
       const int n = lane * RS + k;
       if (pcol0 + c < V && n < N) dst[static_cast<size_t>(pcol0 + c) * N + n] = S[c][k];
     }
+}
+
+// The start state's share of a segment's outputs: y[r][v] += exp(c_r) sum_n C[r][n] S_start[v][n] for the rows of one
+// segment, one head and a block of kFinCols value columns.  A plain tiled fp32 product: both operands pass through shared
+// memory state-coordinate-major in steps of kFinK, a thread owns 8 rows x 8 columns.
+constexpr int kFinCols = 64, kFinK = 32;
+__global__ void __launch_bounds__(kSsdThreads)
+ssd_finish_kernel(kllm_seq_ssd m, int segs_max, const float* __restrict__ xbc, StepRows rows, float* __restrict__ y,
+                  SsdScratch sc) {
+  const int e = blockIdx.z / segs_max, seg = blockIdx.z % segs_max;
+  if (seg == 0) return;  // the first segment started from the true state
+  const int e_first = rows.ent_first[e], e_count = rows.ent_count[e];
+  if (seg * kSsdSeg >= e_count) return;
+  const int first = e_first + seg * kSsdSeg, count = min(kSsdSeg, e_count - seg * kSsdSeg);
+  const int h = blockIdx.y, N = m.state, V = m.vdim, inner = ssd_inner(m), C = ssd_conv_channels(m);
+  const int c_off = inner + m.groups * N + h / (m.heads / m.groups) * N;
+  const int v0 = blockIdx.x * kFinCols;
+  const float* S = sc.send + (static_cast<size_t>(ssd_segment_id(e_first, e, seg)) * m.heads + h) * V * N;
+  __shared__ __align__(16) float Cs[kFinK][kSsdSeg + 4];
+  __shared__ __align__(16) float Ss[kFinK][kFinCols + 4];
+  const int tr = threadIdx.x / 8 * 8, tc = threadIdx.x % 8 * 8;  // 16 blocks of rows x 8 blocks of columns
+  float acc[8][8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[i][j] = 0.f;
+  for (int k0 = 0; k0 < N; k0 += kFinK) {
+    __syncthreads();
+    for (int i = threadIdx.x; i < kSsdSeg * kFinK; i += kSsdThreads) {
+      const int k = i % kFinK, r = i / kFinK;
+      Cs[k][r] = r < count && k0 + k < N ? xbc[static_cast<size_t>(first + r) * C + c_off + k0 + k] : 0.f;
+    }
+    for (int i = threadIdx.x; i < kFinCols * kFinK; i += kSsdThreads) {
+      const int k = i % kFinK, v = i / kFinK;
+      Ss[k][v] = v0 + v < V && k0 + k < N ? S[static_cast<size_t>(v0 + v) * N + k0 + k] : 0.f;
+    }
+    __syncthreads();
+#pragma unroll 4
+    for (int k = 0; k < kFinK; ++k) {
+      float a[8], b[8];
+      *reinterpret_cast<float4*>(a) = *reinterpret_cast<const float4*>(&Cs[k][tr]);
+      *reinterpret_cast<float4*>(a + 4) = *reinterpret_cast<const float4*>(&Cs[k][tr + 4]);
+      *reinterpret_cast<float4*>(b) = *reinterpret_cast<const float4*>(&Ss[k][tc]);
+      *reinterpret_cast<float4*>(b + 4) = *reinterpret_cast<const float4*>(&Ss[k][tc + 4]);
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int r = tr + i;
+    if (r >= count) continue;
+    const float dec = expf(sc.cum[static_cast<size_t>(first + r) * m.heads + h]);
+    float* yr = y + static_cast<size_t>(first + r) * inner + h * V + v0 + tc;
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      if (v0 + tc + j < V) yr[j] += dec * acc[i][j];
+  }
 }
 
 // One thread per (entry, head, value column, state coordinate): the start state of every segment after the first, and the
@@ -389,8 +429,11 @@ int launch_ssd_scan(const kllm_seq_ssd& m, const float* proj, const float* xbc, 
   const dim3 cgrid(static_cast<unsigned>((per + 127) / 128), rows.n_entries);
   ssd_carry_kernel<<<cgrid, 128, 0, s>>>(m, state, rows, ent_seq, sc);
   count_launch();
-  KLLM_SSD_SCAN(2, sc);
 #undef KLLM_SSD_SCAN
+  static_assert(kSsdThreads == 128 && kSsdSeg == 128, "ssd_finish_kernel: 16 x 8 threads own 8 x 8 outputs of a 128 x 64 tile");
+  const dim3 fgrid((m.vdim + kFinCols - 1) / kFinCols, m.heads, rows.n_entries * l.segs_max);
+  ssd_finish_kernel<<<fgrid, kSsdThreads, 0, s>>>(m, l.segs_max, xbc, rows, y, sc);
+  count_launch();
   return cuda_rc(cudaGetLastError());
 }
 

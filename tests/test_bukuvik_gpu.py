@@ -603,3 +603,27 @@ def test_many_heads_in_single_token_steps(tmp_path):
     t = toks(30, cfg["vocab"], 78)
     logits, _ = run_trace(d, [whole("a", t[:10], end=False)] + single("a", t[10:]))
     assert_rows(np.concatenate(logits), ref_logits(cfg, w, t))
+
+
+@pytest.mark.parametrize("kind,heads,kv_heads", [("diff", 6, 2), ("diff", 5, 5), ("diff", 8, 1), ("left", 6, 2), ("left", 5, 1)])
+def test_bfloat16_prompts_with_other_head_counts(tmp_path, kind, heads, kv_heads):
+    """Three, one and eight query heads per key head on the tensor-core prompt path (a row tile then mixes the rows of
+    several heads), beside a second request and followed by single-token steps."""
+    if kind == "diff":
+        layers = [(bo.diff_mixer(heads=heads, kv_heads=kv_heads, dim=40, vdim=72, rot_dims=24, window=50), 48)]
+    else:
+        layers = [(par(left=dict(heads=heads, kv_heads=kv_heads, dim=40, vdim=24, rot_dims=24, window=50, keep_first=9)), 48)]
+    cfg = bo.make_config(width=64, vocab=80, layers=layers)
+    w = bo.make_weights(cfg, seed=43, sharp=2.0)
+    d = bo.write_model(tmp_path, cfg, w)
+    a, b = toks(150, cfg["vocab"], 44), toks(37, cfg["vocab"], 45)
+    steps = [{"entries": [{"id": "a", "tokens": a[:140], "want": list(range(140))},
+                          {"id": "b", "tokens": b[:27], "want": list(range(27))}]}]
+    for j in range(10):
+        steps.append({"entries": [{"id": "a", "tokens": [a[140 + j]], "want": [0]}, {"id": "b", "tokens": [b[27 + j]], "want": [0]}]})
+    for dtype, tol in (("float32", TOL32), ("bfloat16", TOL16)):
+        logits, _ = run_trace(d, steps, dtype=dtype)
+        got_a = np.concatenate([logits[0][:140]] + [lg[0:1] for lg in logits[1:]])
+        got_b = np.concatenate([logits[0][140:]] + [lg[1:2] for lg in logits[1:]])
+        assert rel_err(got_a, ref_logits(cfg, w, a)) < tol
+        assert rel_err(got_b, ref_logits(cfg, w, b)) < tol
