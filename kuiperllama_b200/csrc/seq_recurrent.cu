@@ -378,15 +378,6 @@ __global__ void delta_prepare_kernel(kllm_seq_delta m, const float* __restrict__
 constexpr int kDeltaThreads = 128;
 constexpr int kDeltaPad = 4;  // floats between the row slices of two lanes in shared memory: their 16-byte loads hit different banks
 
-__device__ __forceinline__ void cp_async4(float* dst, const float* src) {
-  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(dst))), "l"(src));
-}
-__device__ __forceinline__ void cp_async16(float* dst, const float* src) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(dst))), "l"(src));
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
-
 // One CTA: one entry, one head, COLS = kDeltaThreads / L value columns.  L lanes share a column j; lane l holds the rows
 // l * RP .. l * RP + RP - 1 of S[:, j] in registers.  Per row of the entry: S <- g S; u = beta (v_j - S[:, j] . k);
 // S[:, j] += k u; o_j = S[:, j] . q -- every column on its own, the two dot products joined over the column's lanes.

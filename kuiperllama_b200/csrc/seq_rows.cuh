@@ -16,6 +16,16 @@ namespace kllm {
 namespace seq {
 namespace {
 
+// asynchronous copies into shared memory: a chunk of rows is on its way while the one before it is worked on
+__device__ __forceinline__ void cp_async4(float* dst, const float* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(dst))), "l"(src));
+}
+__device__ __forceinline__ void cp_async16(float* dst, const float* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(dst))), "l"(src));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+
 // the entry that holds row t: the last e with ent_first[e] <= t
 __device__ __forceinline__ int entry_of(const StepRows& r, int t) {
   int lo = 0, hi = r.n_entries - 1;

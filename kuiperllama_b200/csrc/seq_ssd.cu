@@ -106,8 +106,9 @@ __device__ __forceinline__ bool join_columns(float (&acc)[CC], int L, int lane, 
 // One CTA: one entry (MODE 0) or one segment of an entry (MODE 1), one head, COLS = blockDim.x / L * CC value columns.
 // L lanes share a block of CC columns; lane l keeps the state coordinates l RS .. l RS + RS - 1 of each of them in
 // registers (RS x CC values), so that a row's B and C are read once for CC columns and as 16-byte vectors.  Chunks of
-// rows are staged in shared memory (B and C padded with zeros to L RS coordinates, the columns' x, dt and the decay),
-// then walked one row after the other; only the read-out's dot products are joined over the L lanes.
+// rows pass through two buffers in shared memory (B and C padded with zeros to L RS coordinates, the columns' x, dt and
+// the decay): cp.async brings the next chunk while the current one is walked one row after the other; only the read-out's
+// dot products are joined over the L lanes.
 template <int MODE, int RS, int CC>
 __global__ void __launch_bounds__(kSsdThreads)
 ssd_scan_kernel(kllm_seq_ssd m, int L, int chunk, int segs_max, const float* __restrict__ proj, const float* __restrict__ xbc,
@@ -127,14 +128,33 @@ ssd_scan_kernel(kllm_seq_ssd m, int L, int chunk, int segs_max, const float* __r
   const int b_off = inner + g * N, c_off = inner + m.groups * N + g * N, dt_off = 2 * inner + 2 * m.groups * N + h;
   const float rate = m.a[h], skip = m.d[h], dt_bias = m.dt_bias[h];
 
+  // two buffers of a chunk of rows each: B | C | x | dt (raw, then the step size) | decay
   extern __shared__ __align__(16) float sm[];
-  float* B_s = sm;                    // [chunk][Ns]
-  float* C_s = B_s + chunk * Ns;      // [chunk][Ns]
-  float* x_s = C_s + chunk * Ns;      // [chunk][COLS]
-  float* y_s = x_s + chunk * COLS;    // [chunk][COLS]
-  float* dt_s = y_s + chunk * COLS;   // [chunk]
-  float* dec_s = dt_s + chunk;        // [chunk]: exp(a dt)
-  float* cum_s = dec_s + chunk;       // [chunk]: c_t
+  const int per_buf = chunk * (2 * Ns + COLS + 2);
+  float* y_s = sm + 2 * per_buf;      // [chunk][COLS]
+  float* cum_s = y_s + chunk * COLS;  // [chunk]: c_t
+  // the rows r0 .. of the entry on their way into buffer b (coordinates beyond N and columns beyond V are zeros, written
+  // by plain stores: the buffer was last read before the barrier that precedes this call)
+  auto fetch = [&](int b, int r0) {
+    const int nr = min(chunk, count - r0);
+    float* B_s = sm + b * per_buf;
+    float* C_s = B_s + chunk * Ns;
+    float* x_s = C_s + chunk * Ns;
+    float* dt_s = x_s + chunk * COLS;
+    for (int i = threadIdx.x; i < nr * Ns; i += nthreads) {
+      const int n = i % Ns;
+      const float* row = xbc + static_cast<size_t>(first + r0 + i / Ns) * C;
+      if (n < N) cp_async4(B_s + i, row + b_off + n), cp_async4(C_s + i, row + c_off + n);
+      else B_s[i] = 0.f, C_s[i] = 0.f;
+    }
+    for (int i = threadIdx.x; i < nr * COLS; i += nthreads) {
+      const int pc = blockIdx.x * COLS + i % COLS;
+      if (pc < V) cp_async4(x_s + i, xbc + static_cast<size_t>(first + r0 + i / COLS) * C + h * V + pc);
+      else x_s[i] = 0.f;
+    }
+    for (int i = threadIdx.x; i < nr; i += nthreads) cp_async4(dt_s + i, proj + static_cast<size_t>(first + r0 + i) * P + dt_off);
+    cp_async_commit();
+  };
 
   float S[CC][RS];
   const size_t sid = MODE == 0 ? 0 : ssd_segment_id(e_first, e, seg);
@@ -150,21 +170,19 @@ ssd_scan_kernel(kllm_seq_ssd m, int L, int chunk, int segs_max, const float* __r
       }
   }
   float cum = 0.f;  // the sum of a dt since the segment's start (the same in every thread)
-  for (int r0 = 0; r0 < count; r0 += chunk) {
+  fetch(0, 0);
+  for (int r0 = 0, b = 0; r0 < count; r0 += chunk, b ^= 1) {
     const int nr = min(chunk, count - r0);
-    __syncthreads();
-    for (int i = threadIdx.x; i < nr * Ns; i += nthreads) {
-      const int n = i % Ns;
-      const size_t row = static_cast<size_t>(first + r0 + i / Ns) * C;
-      B_s[i] = n < N ? xbc[row + b_off + n] : 0.f;
-      C_s[i] = n < N ? xbc[row + c_off + n] : 0.f;
-    }
-    for (int i = threadIdx.x; i < nr * COLS; i += nthreads) {
-      const int pc = blockIdx.x * COLS + i % COLS;
-      x_s[i] = pc < V ? xbc[static_cast<size_t>(first + r0 + i / COLS) * C + h * V + pc] : 0.f;
-    }
+    const float* B_s = sm + b * per_buf;
+    const float* C_s = B_s + chunk * Ns;
+    const float* x_s = C_s + chunk * Ns;
+    float* dt_s = sm + b * per_buf + 2 * chunk * Ns + chunk * COLS;
+    float* dec_s = dt_s + chunk;
+    cp_async_wait_all();
+    __syncthreads();  // the chunk has landed; the chunk before it (the other buffer, y_s) has been used up
+    if (r0 + chunk < count) fetch(b ^ 1, r0 + chunk);
     for (int i = threadIdx.x; i < nr; i += nthreads) {
-      const float dt = softplusf(proj[static_cast<size_t>(first + r0 + i) * P + dt_off] + dt_bias);
+      const float dt = softplusf(dt_s[i] + dt_bias);
       dt_s[i] = dt;
       dec_s[i] = expf(rate * dt);
     }
@@ -402,7 +420,7 @@ int launch_ssd_scan(const kllm_seq_ssd& m, const float* proj, const float* xbc, 
   const bool segments = max_count > kSsdParallelFrom && scratch != nullptr;
   const int longest = segments ? kSsdSeg : max_count;
   auto smem_for = [&](int chunk) {
-    return static_cast<size_t>(chunk) * (2 * l.L * RS + 2 * COLS + 3) * sizeof(float);
+    return static_cast<size_t>(chunk) * (2 * (2 * l.L * RS + COLS + 2) + COLS + 1) * sizeof(float);  // two buffers, y, c_t
   };
   int chunk = 32;
   while (chunk > 1 && (smem_for(chunk) > 48 * 1024 || chunk / 2 >= longest)) chunk /= 2;
