@@ -98,6 +98,7 @@ CASES = {
     "right_one_state": [(par(right=dict(heads=2, vdim=7, state=1, groups=1, norm_groups=7)), None)],
     "right_many_states": [(par(right=dict(heads=2, vdim=3, state=100, groups=2, conv=4, norm_groups=3)), None)],
     "right_states_over_lanes": [(par(right=dict(heads=2, vdim=40, state=40, groups=1, conv=4, norm_groups=5)), None)],
+    "right_states_beyond_256": [(par(right=dict(heads=2, vdim=6, state=300, groups=1, conv=2, norm_groups=2)), None)],
     "right_no_filter": [(par(right=dict(conv=1)), None)],
     "right_long_filter": [(par(right=dict(conv=7)), None)],
     "right_one_norm_part": [(par(right=dict(norm_groups=1)), None)],
@@ -627,3 +628,16 @@ def test_bfloat16_prompts_with_other_head_counts(tmp_path, kind, heads, kv_heads
         got_b = np.concatenate([logits[0][140:]] + [lg[1:2] for lg in logits[1:]])
         assert rel_err(got_a, ref_logits(cfg, w, a)) < tol
         assert rel_err(got_b, ref_logits(cfg, w, b)) < tol
+
+
+def test_wide_states_in_segments(tmp_path):
+    """More than 256 state coordinates (16 per lane, two columns a thread) in an entry long enough to be cut into segments,
+    then single-token steps."""
+    cfg = bo.make_config(width=32, vocab=40, layers=[(par(right=dict(heads=2, vdim=5, state=270, groups=2, conv=3, norm_groups=1)), None)])
+    w = bo.make_weights(cfg, seed=95)
+    mute(w, 0, "left")
+    d = bo.write_model(tmp_path, cfg, w)
+    t = toks(3 + 290 + 4, cfg["vocab"], 96)
+    steps = [whole("a", t[:3], end=False), whole("a", t[3:293], end=False)] + single("a", t[293:])
+    logits, _ = run_trace(d, steps, max_tokens=512)
+    assert_rows(np.concatenate(logits), ref_logits(cfg, w, t))
