@@ -376,8 +376,8 @@ class BukuvikShape:
     s_groups: int
     s_norm_groups: int
     taps: int = 4
-    softcap: float = 50.0
-    diff: float = 0.3
+    softcap: float = 30.0
+    diff: float = 0.2
     eps: float = 1e-5
 
     @property
@@ -732,7 +732,7 @@ class SeqEngine:
         layers = (Layer * shape.layers)()
         for L, (mix, ff) in zip(layers, shape.pattern):
             L.pre_mixer, L.pre_ff = Norm(None, None, 2), Norm(None, None, 2)
-            L.post_mixer = out_norm(0.7)
+            L.post_mixer = out_norm(0.8)
             L.mixer_scale = L.mixer2_scale = 1.0
             if mix == "attention":
                 L.mixer_kind = 1
@@ -742,7 +742,7 @@ class SeqEngine:
                 a.qk_norm, a.softcap, a.differential = 1, shape.softcap, 1
                 a.q_norm_w = f32(shape.dim, std=0.05, mean=1.0).data_ptr()
                 a.k_norm_w = f32(shape.dim, std=0.05, mean=1.0).data_ptr()
-                a.rope_freq, a.rope_mag = frequencies(shape.rot_dims, 2.5e5), 1.0
+                a.rope_freq, a.rope_mag = frequencies(shape.rot_dims, 1e6), 1.0
                 a.diff_lambda, a.diff_out_scale = 0.8, 1.0 - shape.diff
             else:
                 L.mixer_kind, L.mixer2_kind = 1, 6
@@ -753,7 +753,7 @@ class SeqEngine:
                           shape.n_in("left"))
                 a.qk_norm, a.keep_first = 2, shape.l_keep_first
                 a.scale = 2.0 * shape.l_dim ** -0.5
-                a.rope_freq, a.rope_mag = frequencies(shape.l_rot_dims, 5e5, 8.0), 0.1 * math.log(8.0) + 1.0
+                a.rope_freq, a.rope_mag = frequencies(shape.l_rot_dims, 1e4, 4.0), 0.1 * math.log(4.0) + 1.0
                 b = L.ssd
                 b.heads, b.vdim, b.state, b.groups = shape.s_heads, shape.s_vdim, shape.s_state, shape.s_groups
                 b.conv_taps, b.norm_groups = shape.taps, shape.s_norm_groups
@@ -770,7 +770,7 @@ class SeqEngine:
                 b.w_out = rnd(W, inner, std=inner ** -0.5).data_ptr()
             L.ff_kind = 2 if ff else 0
             if ff:
-                L.post_ff = out_norm(0.7)
+                L.post_ff = out_norm(0.8)
                 d = L.dense
                 d.ff, d.act = ff, 1
                 d.up = rnd(ff, W, std=W ** -0.5).data_ptr()
