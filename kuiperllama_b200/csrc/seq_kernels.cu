@@ -806,11 +806,11 @@ __global__ void attention_merge_kernel(int heads, int vdim, int splits, const fl
   }
 }
 
-// Differential attention.  One CTA per (token, head): the key splits of the head's two maps are joined (each map has a
+// Differential attention, few rows (single-token steps).  One CTA per (token, head), a thread per value: the key splits of the head's two maps are joined (each map has a
 // softmax of its own), o = a1 - lambda * a2, then o / sqrt(mean(o^2) + eps) * out_scale over the head's values and the
 // output gate.  The maps of head h (key group g = h / rep) lie at attention heads (2 g + m) * rep + h % rep.
 template <typename AT>
-__global__ void diff_merge_kernel(int heads, int rep, int vdim, int splits, const float* __restrict__ ws,
+__global__ void diff_merge_row_kernel(int heads, int rep, int vdim, int splits, const float* __restrict__ ws,
                                   const float* __restrict__ gates, int gate_kind, float lambda, float out_scale, float eps,
                                   AT* __restrict__ out) {
   extern __shared__ float orow[];  // [vdim]
@@ -847,6 +847,61 @@ __global__ void diff_merge_kernel(int heads, int rep, int vdim, int splits, cons
   for (int d = threadIdx.x; d < vdim; d += blockDim.x) {
     const float gate = gates && gate_kind == KLLM_SEQ_GATE_ELEMENT ? gates[th * vdim + d] : head_gate;
     out[th * vdim + d] = from_f<AT>(orow[d] * rinv * gate);
+  }
+}
+
+// Differential attention, many rows (prompts).  One warp per (token, head): the key splits of the head's two maps are joined (each map has a
+// softmax of its own), o = a1 - lambda * a2, then o / sqrt(mean(o^2) + eps) * out_scale over the head's values and the
+// output gate.  The maps of head h (key group g = h / rep) lie at attention heads (2 g + m) * rep + h % rep.  A lane keeps
+// its values (vdim <= 256: at most kDiffPerLane) in registers between the two sweeps.
+constexpr int kDiffWarps = 4, kDiffPerLane = 8;
+constexpr int kDiffRowsForWarps = 1024;  // (token, head) rows from which the warp form is used
+template <typename AT>
+__global__ void diff_merge_kernel(int n_rows, int heads, int rep, int vdim, int splits, const float* __restrict__ ws,
+                                  const float* __restrict__ gates, int gate_kind, float lambda, float out_scale, float eps,
+                                  AT* __restrict__ out) {
+  const int row = blockIdx.x * kDiffWarps + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (row >= n_rows) return;
+  const int t = row / heads, h = row % heads;
+  const int pstride = vdim + 2;
+  const float* p[2];
+  float M[2], L[2];
+  for (int m = 0; m < 2; ++m) {
+    const size_t th = static_cast<size_t>(t) * heads * 2 + ((h / rep) * 2 + m) * rep + h % rep;
+    p[m] = ws + th * splits * pstride;
+    M[m] = -INFINITY, L[m] = 0.f;
+    for (int s = 0; s < splits; ++s) M[m] = fmaxf(M[m], p[m][s * pstride]);
+    for (int s = 0; s < splits; ++s) {
+      const float mm = p[m][s * pstride];
+      if (mm > -INFINITY) L[m] += p[m][s * pstride + 1] * expf(mm - M[m]);
+    }
+  }
+  float vals[kDiffPerLane];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < kDiffPerLane; ++i) {
+    const int d = lane + 32 * i;
+    vals[i] = 0.f;
+    if (d >= vdim) continue;
+    float o[2] = {0.f, 0.f};
+    for (int m = 0; m < 2; ++m)
+      for (int s = 0; s < splits; ++s) {
+        const float mm = p[m][s * pstride];
+        if (mm > -INFINITY) o[m] += p[m][s * pstride + 2 + d] * expf(mm - M[m]);
+      }
+    vals[i] = o[0] / L[0] - lambda * (o[1] / L[1]);
+    ss = fmaf(vals[i], vals[i], ss);
+  }
+  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  const float rinv = out_scale / sqrtf(ss / static_cast<float>(vdim) + eps);
+  const size_t th = static_cast<size_t>(row);
+  const float head_gate = gates && gate_kind == KLLM_SEQ_GATE_HEAD ? gates[th] : 1.0f;
+#pragma unroll
+  for (int i = 0; i < kDiffPerLane; ++i) {
+    const int d = lane + 32 * i;
+    if (d >= vdim) continue;
+    const float gate = gates && gate_kind == KLLM_SEQ_GATE_ELEMENT ? gates[th * vdim + d] : head_gate;
+    out[th * vdim + d] = from_f<AT>(vals[i] * rinv * gate);
   }
 }
 
@@ -1089,9 +1144,17 @@ int launch_diff_merge(int dtype, const AttnShape& a, int splits, const float* ws
                       float out_scale, float eps, void* out, int T, cudaStream_t s) {
   if (v_share_of(a) != 2 || a.heads % 2 || a.kv_heads % 2 || a.sink != nullptr) return KLLM_E_UNSUPPORTED;
   const int heads = a.heads / 2;
-  const int threads = a.vdim <= 64 ? 64 : 128;
-  KLLM_SEQ_DISPATCH(dtype, (diff_merge_kernel<AT><<<T * heads, threads, a.vdim * sizeof(float), s>>>(
-                               heads, a.heads / a.kv_heads, a.vdim, splits, ws, a.gate ? gates : nullptr, a.gate, lambda,
+  if (a.vdim > 32 * kDiffPerLane) return KLLM_E_UNSUPPORTED;
+  const int n_rows = T * heads;
+  if (n_rows < kDiffRowsForWarps) {  // latency matters more than the CTA count: a thread per value
+    const int threads = a.vdim <= 64 ? 64 : 128;
+    KLLM_SEQ_DISPATCH(dtype, (diff_merge_row_kernel<AT><<<n_rows, threads, a.vdim * sizeof(float), s>>>(
+                                 heads, a.heads / a.kv_heads, a.vdim, splits, ws, a.gate ? gates : nullptr, a.gate, lambda,
+                                 out_scale, eps, static_cast<AT*>(out))));
+    return done();
+  }
+  KLLM_SEQ_DISPATCH(dtype, (diff_merge_kernel<AT><<<(n_rows + kDiffWarps - 1) / kDiffWarps, 32 * kDiffWarps, 0, s>>>(
+                               n_rows, heads, a.heads / a.kv_heads, a.vdim, splits, ws, a.gate ? gates : nullptr, a.gate, lambda,
                                out_scale, eps, static_cast<AT*>(out))));
   return done();
 }
